@@ -14,7 +14,7 @@ import torch
 _PKG_ROOT = Path(__file__).resolve().parent.parent
 LIB_PATH = Path(os.environ.get("CVLLM_LIB", _PKG_ROOT / "lib" / "libcompactor_sm100.so"))
 
-CVLLM_F16, CVLLM_BF16, CVLLM_F32_ACCUM = 0, 1, 2
+CVLLM_F16, CVLLM_BF16, CVLLM_F32_ACCUM, CVLLM_F32 = 0, 1, 2, 3
 
 _i, _i64, _f, _p, _sz, _u32 = C.c_int, C.c_int64, C.c_float, C.c_void_p, C.c_size_t, C.c_uint32
 
@@ -77,6 +77,16 @@ _SIGNATURES = {
     "cvllm_snapkv_scores": (_i, [_p, _p, _i64, _i64, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i,
                                  _i, _p, _i, _p, _sz, _p]),
     "cvllm_selftest_umma": (_i, [_p, _p, _p, _i, _u32, _u32, _i, _p]),
+    "cvllm_sandwich_norm": (_i, [_p, _i64, _i, _p, _p, _i64, _p, _p, _i64, _i, _i, _i, _f, _p]),
+    "cvllm_gated_act": (_i, [_p, _i64, _p, _i64, _i64, _i, _i, _i, _p]),
+    "cvllm_moe_route": (_i, [_p, _i64, _p, _i, _i, _i, _i, _i, _p, _p, _p]),
+    "cvllm_moe_combine": (_i, [_p, _p, _p, _i, _p, _i, _p, _p, _p, _i64, _i, _i, _p]),
+    "cvllm_qknorm_store": (_i, [_p, _i64, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
+                                _i, _i, _i, _i, _i, _i, _i, _p]),
+    "cvllm_bias_attn_varlen": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _f, _p,
+                                    _i, _i, _i, _i, _i, _i, _i, _p]),
+    "cvllm_bias_attn_decode": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _i, _i, _f, _p,
+                                    _i, _i, _i, _i, _i, _i, _i, _p]),
 }
 
 _lib = None
@@ -138,6 +148,15 @@ def dtype_code(dt: torch.dtype) -> int:
     if dt == torch.float16:
         return CVLLM_F16
     raise TypeError(f"cvllm kernels support float16/bfloat16, got {dt}")
+
+
+def block_dtype_code(dt: torch.dtype) -> int:
+    """dtype code of the model-block and biased-attention entry points (bfloat16 or float32 storage)."""
+    if dt == torch.bfloat16:
+        return CVLLM_BF16
+    if dt == torch.float32:
+        return CVLLM_F32
+    raise TypeError(f"this kernel family takes bfloat16/float32, got {dt}")
 
 
 _WORKSPACES: dict = {}

@@ -33,6 +33,7 @@ class LLMConfig:
     leverage_sketch_size: int = 48
     attention_backend: AttentionBackend = AttentionBackend.COMPACTOR_TRITON
     show_progress_bar: bool = True
+    dtype: Any = None            # overrides the model config's torch_dtype ("bfloat16", "float32" or a torch.dtype)
 
     def __post_init__(self):
         if self.path is not None and not os.path.isdir(self.path):
@@ -40,7 +41,15 @@ class LLMConfig:
         if self.tensor_parallel_size <= 0 or self.tensor_parallel_size > 8:
             raise ValueError("tensor_parallel_size must be >= 1 and <= 8")
         if self.hf_config is None:
-            from transformers import AutoConfig
+            from compactor_vllm.config.model_config import load_model_config
 
-            self.hf_config = AutoConfig.from_pretrained(self.model)
+            # a folder with a config.json of one of the engine's own designs is read here, the rest by transformers
+            self.hf_config = load_model_config(self.path if self.path is not None else self.model)
+        if self.dtype is not None:
+            import torch
+
+            dt = getattr(torch, self.dtype) if isinstance(self.dtype, str) else self.dtype
+            if not isinstance(dt, torch.dtype):
+                raise ValueError(f"dtype {self.dtype!r} is not a torch dtype")
+            self.dtype = self.hf_config.torch_dtype = dt
         self.max_model_len = min(self.max_model_len, self.hf_config.max_position_embeddings)

@@ -1,0 +1,149 @@
+"""Model configurations the engine reads itself (a folder's config.json), beside the HF ones `AutoConfig` resolves.
+
+`load_model_config(path)` looks at config.json: a top-level "architecture" naming one of the designs below is
+parsed here; anything else goes to transformers.  The result carries the attribute names the cache manager and the
+runner read from an HF config (`model_type`, `torch_dtype`, `vocab_size`, `max_position_embeddings`, ...).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, List, Optional, Tuple
+
+import torch
+
+
+@dataclass
+class AttentionMixerConfig:
+    """Grouped-query attention without rotation: per-head RMS norm of q and k, a linear distance bias
+    (slope of head h = 2 ** (-8 (h + 1) / heads)), a chunk mask and a softmax sink."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    chunk: int = 0            # keys are visible inside the query's chunk of this many positions; 0 = no chunking
+
+    @classmethod
+    def from_json(cls, m: dict) -> "AttentionMixerConfig":
+        mask = m.get("mask") or {}
+        dim = int(m["dim"])
+        return cls(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=dim,
+                   vdim=int(m.get("vdim", dim)), scale=float(m.get("scale", dim ** -0.5)),
+                   chunk=int(mask.get("size", 0) or 0))
+
+
+@dataclass
+class FeedForwardConfig:
+    """kind "dense": down(gelu_tanh(gate h) * up h).  kind "moe": `experts` silu-gated experts of size `ff` plus
+    `identity` experts that return their input; every token takes `top` of them (see layers/moe.py)."""
+    kind: str
+    ff: int
+    experts: int = 0
+    identity: int = 0
+    top: int = 0
+    groups: int = 1
+    keep: int = 1
+    shared_ff: int = 0        # 0 = no shared expert
+
+    @classmethod
+    def from_json(cls, m: Optional[dict]) -> Optional["FeedForwardConfig"]:
+        if m is None:
+            return None
+        kind = m.get("kind", "dense")
+        if kind == "dense":
+            return cls(kind="dense", ff=int(m["ff"]))
+        if kind != "moe":
+            raise ValueError(f"unknown feed-forward kind {kind!r}")
+        r = m["router"]
+        g = r.get("groups") or {}
+        shared = m.get("shared") or {}
+        return cls(kind="moe", ff=int(m["expert"]["ff"]), experts=int(r["experts"]), identity=int(r.get("identity", 0)),
+                   top=int(r["top"]), groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))),
+                   shared_ff=int(shared.get("ff", 0) or 0))
+
+
+@dataclass
+class MovolornLayerConfig:
+    mixer_type: str
+    mixer: AttentionMixerConfig
+    mlp: Optional[FeedForwardConfig]
+
+
+@dataclass
+class MovolornConfig:
+    """config.json of a Movolorn model: `vocab`, `width`, `embedding.scale`, `norm.eps`, `layers` (each with `type`,
+    `mixer`, `mlp`), `loop` (`start`, `stop`, `times`: layers start..stop-1 run `times` times in a row with the same
+    weights and a cache of their own per pass)."""
+    vocab_size: int
+    hidden_size: int
+    embedding_scale: float
+    rms_norm_eps: float
+    layers: List[MovolornLayerConfig]
+    loop: Optional[Tuple[int, int, int]] = None
+    torch_dtype: Any = torch.bfloat16
+    max_position_embeddings: int = 1 << 30      # positions enter through distances only: no table to outgrow
+    model_type: str = "movolorn"
+    tie_word_embeddings: bool = False
+    raw: dict = field(default_factory=dict, repr=False)
+
+    @classmethod
+    def from_json(cls, c: dict) -> "MovolornConfig":
+        layers = []
+        for entry in c["layers"]:
+            kind = entry.get("type", "attention")
+            if kind != "attention":
+                raise ValueError(f"unknown mixer type {kind!r}")
+            layers.append(MovolornLayerConfig(kind, AttentionMixerConfig.from_json(entry["mixer"]),
+                                              FeedForwardConfig.from_json(entry.get("mlp"))))
+        lp = c.get("loop")
+        loop = (int(lp["start"]), int(lp["stop"]), int(lp.get("times", 1))) if lp else None
+        if loop is not None and not (0 <= loop[0] <= loop[1] <= len(layers) and loop[2] >= 1):
+            raise ValueError(f"bad loop {loop} for {len(layers)} layers")
+        return cls(vocab_size=int(c["vocab"]), hidden_size=int(c["width"]),
+                   embedding_scale=float((c.get("embedding") or {}).get("scale", 1.0)),
+                   rms_norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)), layers=layers, loop=loop, raw=c)
+
+    # ---- layer runs: the order in which layers execute, one cache layer per run ----------------------
+    @property
+    def layer_runs(self) -> List[int]:
+        n = len(self.layers)
+        if self.loop is None:
+            return list(range(n))
+        start, stop, times = self.loop
+        return list(range(start)) + list(range(start, stop)) * times + list(range(stop, n))
+
+    # ---- the names the cache manager reads from an HF config ----------------------------------------
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layer_runs)
+
+    @property
+    def num_key_value_heads(self) -> int:
+        return max(l.mixer.kv_heads for l in self.layers)
+
+    @property
+    def num_attention_heads(self) -> int:
+        return max(l.mixer.heads for l in self.layers)
+
+    @property
+    def head_dim(self) -> int:
+        return max(l.mixer.dim for l in self.layers)
+
+
+ARCHITECTURES = {"Movolorn": MovolornConfig}
+
+
+def load_model_config(path: str):
+    """config.json of `path` -> a config object; designs of ARCHITECTURES are parsed here, the rest by transformers."""
+    cfg_file = os.path.join(path, "config.json")
+    if os.path.isfile(cfg_file):
+        with open(cfg_file) as f:
+            raw = json.load(f)
+        arch = raw.get("architecture")
+        if isinstance(arch, str) and arch in ARCHITECTURES:
+            return ARCHITECTURES[arch].from_json(raw)
+    from transformers import AutoConfig
+
+    return AutoConfig.from_pretrained(path)

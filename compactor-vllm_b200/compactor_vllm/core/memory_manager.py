@@ -87,22 +87,40 @@ def activation_token_budget(snap: MemorySnapshot, frac: float, *, warmup_tokens:
 
 
 class SlotMap:
-    """seq_id -> cache slot.  Slots come from (and go back to) the paged cache's free list."""
+    """seq_id -> cache slot.  Slots come from (and go back to) the paged cache's free list.  With several caches
+    (`acquire_all` / `release_all`: one per cache geometry of a model) every cache hands out the same slot, because
+    all of them see the same sequence of acquisitions and releases."""
 
     def __init__(self):
         self.by_seq: Dict[int, int] = {}
 
     def acquire(self, cache: PagedKVCache, seq_id: int) -> Optional[int]:
+        return self.acquire_all([cache], seq_id)
+
+    def acquire_all(self, caches: Sequence[PagedKVCache], seq_id: int) -> Optional[int]:
         slot = self.by_seq.get(seq_id)
         if slot is None:
-            slot = cache.new_batch()
-            if slot is None:
-                return None
-            self.by_seq[seq_id] = slot = int(slot)
+            got = []
+            for cache in caches:
+                s = cache.new_batch()
+                if s is None:           # give back what the earlier caches granted
+                    for c, g in zip(caches, got):
+                        c.free_batch(g)
+                    return None
+                got.append(int(s))
+            assert len(set(got)) == 1, f"cache groups out of step: slots {got}"
+            self.by_seq[seq_id] = slot = got[0]
         return slot
 
     def release(self, cache: PagedKVCache, seq_id: int) -> None:
-        cache.free_batch(self.by_seq.pop(seq_id, None))
+        self.release_all([cache], seq_id)
+
+    def release_all(self, caches: Sequence[PagedKVCache], seq_id: int) -> None:
+        slot = self.by_seq.pop(seq_id, None)
+        if slot is None:
+            return
+        for cache in caches:
+            cache.free_batch(slot)
 
 
 class KVCacheManager:
@@ -120,6 +138,7 @@ class KVCacheManager:
         self.max_pages_per_batch = -(-self.max_model_len // self.page_size)
         self.num_pages: Optional[int] = None
         self.paged_cache: Optional[PagedKVCache] = None
+        self.paged_caches: List[PagedKVCache] = []     # every cache geometry of the model; [paged_cache] as a rule
         self.max_batched_tokens: Optional[int] = None
         self._slots = SlotMap()
 
@@ -152,10 +171,12 @@ class KVCacheManager:
     def init_cache(self, model: nn.Module, num_pages: Optional[int] = None, device_allocator: bool = False):
         """Size the cache (unless `num_pages` is given), allocate it and hand every attention layer its views.
         device_allocator=True: the GPU-resident page allocator (same surface, same page ids)."""
+        cache_type = DevicePagedKVCache if device_allocator else PagedKVCache
+        if hasattr(model, "cache_specs"):
+            return self._init_cache_from_specs(model.cache_specs(), num_pages, cache_type)
         if num_pages is None:
             num_pages = self.get_num_pages(self.gpu_frac, self.max_pages_per_batch)
         self.num_pages = int(num_pages)
-        cache_type = DevicePagedKVCache if device_allocator else PagedKVCache
         self.paged_cache = cache_type(
             num_layers=self.num_layers, max_logical_pages_per_head=int(self.max_pages_per_batch),
             num_pages=self.num_pages, page_size=self.page_size, H_kv=self.num_kv_heads, head_dim=self.head_dim,
@@ -164,10 +185,54 @@ class KVCacheManager:
             attn = layer.self_attn.attn
             attn.k_cache, attn.v_cache, attn.page_table, attn.bh_seq_lens = self.paged_cache.layer_slices(index)
             attn.page_size = self.page_size
+        self.paged_caches = [self.paged_cache]
+
+    def _init_cache_from_specs(self, specs, num_pages: Optional[int], cache_type) -> None:
+        """A model that lists its cache layers itself (`cache_specs()`: one (attention module, kv heads, key size,
+        value size) per cache layer, e.g. one per pass of a looped layer).  Layers of equal geometry share one paged
+        cache; `num_pages` counts pages PER KV HEAD and layer (a sequence of n tokens takes ceil(n / page_size) of
+        them), so that one number fits every geometry."""
+        elem = torch.empty((), dtype=self.model_dtype).element_size()
+        groups: Dict[Tuple[int, int, int], list] = {}
+        for attn, heads, dim, vdim in specs:
+            groups.setdefault((int(heads), int(dim), int(vdim)), []).append(attn)
+        if num_pages is None:
+            snap = MemorySnapshot.capture()
+            budget = int(snap.total * self.gpu_frac * _SAFETY) - snap.used - snap.transient
+            tables = sum(table_bytes(len(a), self.max_num_batches, h, self.max_pages_per_batch)
+                         for (h, _, _), a in groups.items())
+            per_page = sum(len(a) * h * self.page_size * (d + dv) * elem for (h, d, dv), a in groups.items())
+            if budget - tables < per_page:
+                raise RuntimeError(f"Insufficient memory for KV cache: {budget} bytes after tables of {tables}")
+            num_pages = (budget - tables) // per_page
+        self.num_pages = int(num_pages)
+        self.paged_caches = []
+        for (heads, dim, vdim), attns in groups.items():
+            cache = cache_type(
+                num_layers=len(attns), max_logical_pages_per_head=int(self.max_pages_per_batch),
+                num_pages=self.num_pages * heads, page_size=self.page_size, H_kv=heads, head_dim=dim,
+                max_num_batches=self.max_num_batches, dtype=self.model_dtype, device=f"cuda:{self.rank}",
+                v_head_dim=vdim)
+            for index, attn in enumerate(attns):
+                attn.k_cache, attn.v_cache, attn.page_table, attn.bh_seq_lens = cache.layer_slices(index)
+                attn.page_size = self.page_size
+            self.paged_caches.append(cache)
+        self.paged_cache = self.paged_caches[0]
 
     @property
     def num_free_batches(self) -> int:
         return len(self.paged_cache.free_batches)
+
+    @property
+    def num_free_tokens(self) -> int:
+        """Tokens a new or growing sequence can still be granted: whole pages per kv head, the fullest layer of the
+        fullest cache counting."""
+        free = []
+        for cache in self.paged_caches:
+            per_layer = (cache.free_count.tolist() if isinstance(cache, DevicePagedKVCache)
+                         else list(map(len, cache.free_pages)))
+            free.append(min(per_layer) // cache.H_kv)
+        return min(free) * self.page_size
 
     @property
     def num_free_pages(self) -> int:
@@ -186,22 +251,23 @@ class KVCacheManager:
         with its sequence — the scheduler retries or frees."""
         slots: List[int] = []
         for seq_id, tokens in zip(seq_ids, max_positions):
-            slot = self._slots.acquire(self.paged_cache, seq_id)
+            slot = self._slots.acquire_all(self.paged_caches, seq_id)
             if slot is None:
                 logger.warning("no free cache slot for sequence %s", seq_id)
                 return False, None
-            status = self.paged_cache.reserve_tokens(slot, tokens)
-            if status != KVAllocationStatus.SUCCESS:
-                logger.warning("no room for %d tokens of sequence %s: %s", tokens, seq_id, status)
-                return False, None
+            for cache in self.paged_caches:
+                status = cache.reserve_tokens(slot, tokens)
+                if status != KVAllocationStatus.SUCCESS:
+                    logger.warning("no room for %d tokens of sequence %s: %s", tokens, seq_id, status)
+                    return False, None
             slots.append(slot)
         return True, torch.tensor(slots, dtype=torch.int32, device=self.paged_cache.page_table.device)
 
     def free_sequences(self, seq_ids: Iterable[int]) -> None:
         for seq_id in seq_ids:
-            self._slots.release(self.paged_cache, seq_id)
+            self._slots.release_all(self.paged_caches, seq_id)
 
     def reclaim_pages(self, seq_ids_to_reclaim: Iterable[int], future_reserved_buffer) -> int:
         """Return the pages each sequence holds beyond len + future_reserved_buffer[i] tokens; approximate bytes."""
-        return sum(self.paged_cache.reclaim_pages(self._slots.by_seq[seq_id], future_reserved_buffer[i])
-                   for i, seq_id in enumerate(seq_ids_to_reclaim))
+        return sum(cache.reclaim_pages(self._slots.by_seq[seq_id], future_reserved_buffer[i])
+                   for i, seq_id in enumerate(seq_ids_to_reclaim) for cache in self.paged_caches)

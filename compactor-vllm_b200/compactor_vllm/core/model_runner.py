@@ -11,7 +11,9 @@ multi-process tensor parallelism (`tensor_parallel_size` must be 1), preemption.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+import os
+from collections import deque
+from typing import List, Optional, Sequence as Seq, Tuple
 
 import torch
 
@@ -20,7 +22,7 @@ from compactor_vllm.config.constants import RESERVED_BATCH
 from compactor_vllm.config.engine_config import LLMConfig
 from compactor_vllm.core.memory_manager import KVCacheManager
 from compactor_vllm.layers.sampler import Sampler
-from compactor_vllm.models import MODEL_REGISTRY
+from compactor_vllm.models import MODEL_REGISTRY, registry_key
 from compactor_vllm.utils import arguments as A
 from compactor_vllm.utils.context import CompressionContext, reset_context, set_context
 from compactor_vllm.utils.sequence import Sequence, SequenceStatus
@@ -65,10 +67,18 @@ class ModelRunner:
         assert torch.cuda.is_available(), "no CPU fallback"
         self.config = config
         hf = config.hf_config
-        _check_shape_envelope(hf, config)
+        kind = registry_key(hf)
+        self.mixed_steps = bool(getattr(MODEL_REGISTRY[kind], "mixed_steps", False))
+        if not self.mixed_steps:
+            _check_shape_envelope(hf, config)
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.dtype = hf.torch_dtype if isinstance(hf.torch_dtype, torch.dtype) else torch.bfloat16
-        kind = "qwen3" if "qwen3" in str(getattr(hf, "model_type", "llama")).lower() else "llama"
+        if self.dtype not in ((torch.bfloat16, torch.float32) if self.mixed_steps else (torch.bfloat16, torch.float16)):
+            raise ValueError(f"{kind} models do not run in {self.dtype}")
+        if self.dtype == torch.float32:   # true 32-bit products: no reduced-precision matrix mode
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+            torch.set_float32_matmul_precision("highest")
         prev = torch.get_default_dtype()
         torch.set_default_dtype(self.dtype)  # parameters are born in the model dtype on the GPU
         try:
@@ -76,7 +86,13 @@ class ModelRunner:
                 model = MODEL_REGISTRY[kind](hf)
         finally:
             torch.set_default_dtype(prev)
-        model.init_synthetic_weights(seed)
+        weights = os.path.join(config.path, "model.safetensors") if config.path else None
+        if weights and os.path.isfile(weights) and hasattr(model, "load_weights"):
+            from compactor_vllm.utils.safetensors_io import load_safetensors
+
+            model.load_weights(load_safetensors(weights))
+        else:
+            model.init_synthetic_weights(seed)
         self.model = model.to(self.device).eval()
         self.num_kv_heads = hf.num_key_value_heads
         self.head_dim = getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads
@@ -85,12 +101,13 @@ class ModelRunner:
         self.kv.model_dtype = self.dtype
         self.kv.init_cache(self.model, num_pages=num_pages, device_allocator=device_allocator)
         self.store_stream = torch.cuda.Stream(device=self.device, priority=-1)
-        self.PHI = A.make_phi(self.head_dim, config.leverage_sketch_size, self.dtype, self.device)
+        self.PHI = (None if self.mixed_steps
+                    else A.make_phi(self.head_dim, config.leverage_sketch_size, self.dtype, self.device))
         self.sampler = Sampler()
         self.max_batched_tokens = int(max_batched_tokens or config.max_model_len)
         self.eos = config.eos
         self._graphs: dict = {}
-        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "graph_replays": 0, "bytes_reclaimed": 0}
+        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "graph_replays": 0, "bytes_reclaimed": 0, "steps": 0}
 
     # ------------------------------------------------------------------ prefill
     def _prefill_batches(self, seqs: List[Sequence]) -> List[List[Sequence]]:
@@ -232,10 +249,101 @@ class ModelRunner:
         if s.num_generated_tokens >= s.sampling_params.max_new_tokens or token == self.eos or full:
             s.status = SequenceStatus.FINISHED
 
+    # -------------------------------------------------------------- mixed steps
+    @torch.no_grad()
+    def run_step(self, entries: Seq[Tuple[Sequence, Seq[int]]], rows: Optional[Seq[int]] = None) -> torch.Tensor:
+        """One forward pass over a mixed batch: every entry is (sequence, its next tokens) — a portion of a prompt
+        or a single decoded token — continuing from what earlier steps left in the cache.  Returns the logits of
+        `rows` (indices into the step's packed tokens; None = the last token of every entry).  Room for the new
+        tokens is reserved here; a sequence gets its cache slot at its first entry.  Models with `mixed_steps`."""
+        assert self.mixed_steps, "this model runs whole prompts and single tokens only"
+        dev = self.device
+        lens = [len(t) for _, t in entries]
+        assert lens and min(lens) > 0
+        starts = [s.num_computed_tokens for s, _ in entries]
+        ok, batch_mapping = self.kv.allocate_sequences([s.seq_id for s, _ in entries], lens)
+        if not ok:
+            raise KVCacheExhausted(f"no room for a step of {sum(lens)} tokens ({self.kv.num_free_tokens} tokens free)")
+        T = sum(lens)
+        # one host->device copy for all the step's index vectors
+        pos = [p for st, n in zip(starts, lens) for p in range(st, st + n)]
+        slot_of = [self.kv.seq_id_to_batch[s.seq_id] for s, _ in entries]
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        packed = torch.tensor([t for _, toks in entries for t in toks] + pos
+                              + [sl for sl, n in zip(slot_of, lens) for _ in range(n)] + cu + starts,
+                              dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        ids, positions, token_slot = packed[:T].long(), packed[T:2 * T], packed[2 * T:3 * T]
+        cu_t, start_t = packed[3 * T:3 * T + len(cu)], packed[3 * T + len(cu):]
+        set_context(is_prefill=max(lens) > 1, cu_seqlens_q=cu_t, cu_seqlens_k=cu_t, max_seqlen_q=max(lens),
+                    max_seqlen_k=max(st + n for st, n in zip(starts, lens)), batch_mapping=batch_mapping,
+                    positions_i32=positions, token_slot=token_slot, seq_start=start_t)
+        hidden = self.model(ids, positions.long())
+        row_t = None if rows is None else torch.tensor(list(rows), dtype=torch.int64, device=dev)
+        logits = self.model.compute_logits(hidden, row_t)
+        reset_context()
+        for (s, _), n in zip(entries, lens):
+            s.num_computed_tokens += n
+        self.stats["steps"] += 1
+        self.stats["prefill_tokens"] += sum(n for n in lens if n > 1)
+        return logits
+
+    def release(self, seqs: Seq[Sequence]) -> None:
+        """Give back the slots and pages of finished sequences."""
+        self.kv.free_sequences([s.seq_id for s in seqs])
+
+    @torch.no_grad()
+    def _generate_stepwise(self, seqs: List[Sequence]) -> None:
+        """Continuous batching for models with `mixed_steps`: each step carries one token of every decoding
+        sequence plus portions of waiting prompts up to the step's token budget; a sequence is admitted when a slot
+        and pages for its prompt and its completion are free, and gives them back when it finishes."""
+        waiting, running = deque(seqs), []
+        budget = max(int(self.max_batched_tokens), 1)
+        while waiting or running:
+            while waiting and len(running) < self.config.max_num_seqs and self.kv.num_free_batches > 0:
+                s = waiting[0]
+                n = s.num_prompt_tokens
+                assert 0 < n <= self.config.max_model_len, "prompt longer than max_model_len"
+                need = min(n + s.sampling_params.max_new_tokens, self.config.max_model_len)
+                if need > self.kv.num_free_tokens:
+                    break
+                ok, _ = self.kv.allocate_sequences([s.seq_id], [need])
+                assert ok
+                s.status = SequenceStatus.RUNNING
+                running.append(waiting.popleft())
+            if not running:
+                raise KVCacheExhausted(f"sequence {waiting[0].seq_id} does not fit an empty cache")
+            entries, left = [], budget
+            for s in running:      # decoding sequences first: they take one token each
+                if s.num_computed_tokens >= s.num_prompt_tokens:
+                    entries.append((s, [s.completion_token_ids[-1]]))
+                    left -= 1
+            for s in running:
+                done = s.num_computed_tokens
+                if done < s.num_prompt_tokens and left > 0:
+                    n = min(s.num_prompt_tokens - done, left)
+                    entries.append((s, s.prompt_token_ids[done:done + n]))
+                    left -= n
+            logits = self.run_step(entries)
+            sampled = [i for i, (s, _) in enumerate(entries) if s.num_computed_tokens >= s.num_prompt_tokens]
+            if sampled:
+                temps = torch.tensor([entries[i][0].sampling_params.temperature for i in sampled], device=self.device)
+                toks = self.sampler(logits[torch.tensor(sampled, device=self.device)], temps).tolist()
+                for i, t in zip(sampled, toks):
+                    self._accept(entries[i][0], t)
+            self.stats["decode_steps"] += 1
+            finished = [s for s in running if s.status is SequenceStatus.FINISHED]
+            if finished:
+                self.release(finished)
+                running = [s for s in running if s.status is not SequenceStatus.FINISHED]
+
     # ----------------------------------------------------------------- generate
     @torch.no_grad()
     def generate(self, seqs: List[Sequence], params: BatchCompressionParams) -> None:
         """Fill `completion_token_ids` of every sequence (reference: core/model_runner.py:230-338)."""
+        if self.mixed_steps:
+            return self._generate_stepwise(seqs)
         wave = self.config.max_num_seqs
         for w0 in range(0, len(seqs), wave):
             chunk = seqs[w0:w0 + wave]

@@ -51,6 +51,7 @@ class PagedKVCache(torch.nn.Module):
         max_num_batches: int,
         dtype: torch.dtype,
         device: Union[str, torch.device, int] = "cuda",
+        v_head_dim: Optional[int] = None,
     ):
         super().__init__()
         self.n_pages = num_pages
@@ -60,9 +61,16 @@ class PagedKVCache(torch.nn.Module):
         self.max_pages_per_head = max_logical_pages_per_head
         self.max_num_batches = max_num_batches + 1  # + the reserved slot
         self.head_dim = head_dim
-        self.kv_cache = torch.empty(
-            (2, num_layers, num_pages * self.page_size, head_dim), dtype=dtype, device=device
-        )
+        # values may have another row size than keys (v_head_dim): then K and V are two buffers
+        self.v_head_dim = int(head_dim if v_head_dim is None else v_head_dim)
+        rows = num_pages * self.page_size
+        if self.v_head_dim == head_dim:
+            self.kv_cache = torch.empty((2, num_layers, rows, head_dim), dtype=dtype, device=device)
+            self.k_store, self.v_store = self.kv_cache[0], self.kv_cache[1]
+        else:
+            self.kv_cache = None
+            self.k_store = torch.empty((num_layers, rows, head_dim), dtype=dtype, device=device)
+            self.v_store = torch.empty((num_layers, rows, self.v_head_dim), dtype=dtype, device=device)
         self.page_table = torch.empty(
             (num_layers, self.max_num_batches, self.H_kv, self.max_pages_per_head),
             device=device, dtype=torch.int32,
@@ -145,7 +153,7 @@ class PagedKVCache(torch.nn.Module):
         for page, layer in zip(freed, layers):
             self.pages_indices_per_batch[batch_index][layer].remove(page)
             heapq.heappush(self.free_pages[layer], page)
-        return len(freed) * self.page_size * self.head_dim * self.kv_cache.element_size() * 2
+        return len(freed) * self.page_bytes
 
     def _free_batch_layer(self, layer_index: int, batch_index: int) -> None:
         owned = self.pages_indices_per_batch[batch_index][layer_index]
@@ -165,9 +173,14 @@ class PagedKVCache(torch.nn.Module):
         """(k_cache, v_cache, page_table, bh_seq_lens) views of one layer (:293-313)."""
         assert 0 <= layer < self.num_layers
         return (
-            self.kv_cache[0, layer], self.kv_cache[1, layer],
+            self.k_store[layer], self.v_store[layer],
             self.page_table[layer], self.bh_seq_lens[layer],
         )
+
+    @property
+    def page_bytes(self) -> int:
+        """Bytes of one page of keys plus one page of values."""
+        return self.page_size * (self.head_dim + self.v_head_dim) * self.k_store.element_size()
 
 
 class DevicePagedKVCache(PagedKVCache):
@@ -258,7 +271,7 @@ class DevicePagedKVCache(PagedKVCache):
         self._slot1.fill_(int(batch_index))
         self._freed.zero_()
         self._release(self._slot1, future_reserve_tokens, False, True)
-        return int(self._freed) * self.page_size * self.head_dim * self.kv_cache.element_size() * 2
+        return int(self._freed) * self.page_bytes
 
     def free_batch(self, batch_index: int) -> None:
         self._slot1.fill_(int(batch_index))

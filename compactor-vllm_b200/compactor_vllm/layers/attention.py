@@ -105,3 +105,76 @@ class Attention(nn.Module):
                 STORE_STREAM=context.STORE_STREAM if context.is_prefill else None,
             )
         return o
+
+
+def linear_bias_slopes(num_heads: int, base_exponent: float = 8.0) -> torch.Tensor:
+    """Per-head slopes of a linear distance bias: slope_h = 2 ** (-base_exponent * (h + 1) / num_heads), fp32."""
+    h = torch.arange(1, num_heads + 1, dtype=torch.float64)
+    return torch.pow(torch.tensor(2.0, dtype=torch.float64), -base_exponent * h / num_heads).float()
+
+
+class BiasedChunkAttention(nn.Module):
+    """Attention over the paged cache for models without rotation (csrc/bias_attn.cu):
+
+        score(i, j) = scale * q_i . k_j - slopes[h] * (i - j),   j <= i and floor(i / chunk) == floor(j / chunk)
+        p_j = exp(score_j) / (sink + sum_j exp(score_j))
+
+    with optional per-head RMS norm of q and k (weights shared by all heads), any head sizes (value size may differ
+    from the key size) and bfloat16 or float32 storage.  `slopes` None = no bias, `chunk` 0 = plain causal, `sink`
+    False = plain softmax.  forward() takes the packed projection rows [T, H*D + G*D + G*Dv]: one launch norms q / k
+    and writes k / v to the cache at the tokens' positions, one launch attends — the portion kernel when any
+    sequence of the step brings more than one token, the decode kernel otherwise.  The step's geometry comes from the
+    global context: `positions_i32`, `token_slot`, `cu_seqlens_q`, `seq_start`, `batch_mapping`, `max_seqlen_q`.
+    The cache manager injects the cache views exactly as for `Attention`."""
+
+    def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float, *,
+                 slopes: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False, qk_norm: bool = False,
+                 eps: float = 1e-6):
+        super().__init__()
+        self.num_heads, self.num_kv_heads = int(num_heads), int(num_kv_heads)
+        self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
+        self.scale, self.chunk, self.sink, self.eps = float(scale), int(chunk), bool(sink), float(eps)
+        self.register_buffer("slopes", None if slopes is None else slopes.float().contiguous(), persistent=False)
+        self.q_norm_weight = nn.Parameter(torch.ones(head_dim, dtype=torch.float32)) if qk_norm else None
+        self.k_norm_weight = nn.Parameter(torch.ones(head_dim, dtype=torch.float32)) if qk_norm else None
+        self.k_cache: Optional[torch.Tensor] = None
+        self.v_cache: Optional[torch.Tensor] = None
+        self.page_table: Optional[torch.Tensor] = None
+        self.bh_seq_lens: Optional[torch.Tensor] = None
+        self.page_size: Optional[int] = None
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
+
+    def forward(self, qkv: torch.Tensor) -> torch.Tensor:
+        from compactor_vllm import _native as N
+
+        ctx: Context = get_context()
+        assert self.k_cache is not None, "KV cache must be initialized"
+        T = qkv.shape[0]
+        H, G, D, Dv = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        assert qkv.shape[1] == self.qkv_width and qkv.stride(1) == 1 and qkv.dtype == self.k_cache.dtype
+        dev, code, lib = qkv.device, N.block_dtype_code(qkv.dtype), N.lib()
+        q = torch.empty((T, H, D), dtype=qkv.dtype, device=dev)
+        pt = self.page_table
+        table = (N.ptr(pt), pt.stride(0), pt.stride(1), int(self.page_size))
+        N.check(lib.cvllm_qknorm_store(
+            N.ptr(qkv), qkv.stride(0), N.ptr(self.q_norm_weight), N.ptr(self.k_norm_weight), self.eps,
+            N.ptr(ctx.positions_i32), N.ptr(ctx.token_slot), N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache),
+            *table, N.ptr(self.bh_seq_lens), T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)), "cvllm_qknorm_store")
+        out = torch.empty((T, H, Dv), dtype=qkv.dtype, device=dev)
+        if ctx.is_prefill:
+            B = ctx.batch_mapping.numel()
+            N.check(lib.cvllm_bias_attn_varlen(
+                N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache), *table, N.ptr(ctx.cu_seqlens_q),
+                N.ptr(ctx.seq_start), N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink),
+                self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, code, N.stream(dev)),
+                "cvllm_bias_attn_varlen")
+        else:
+            assert ctx.batch_mapping.numel() == T
+            N.check(lib.cvllm_bias_attn_decode(
+                N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache), *table, N.ptr(ctx.positions_i32),
+                N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), self.scale, N.ptr(out),
+                T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)), "cvllm_bias_attn_decode")
+        return out.view(T, H * Dv)

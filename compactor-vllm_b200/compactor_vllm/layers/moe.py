@@ -1,0 +1,101 @@
+"""Feed-forward blocks: a gated dense layer and a routed mixture of experts.
+
+Matrix products are library GEMMs (`torch.nn.functional.linear`), as in the other models; the gated activation,
+the router's choice and the weighted combine are kernels of the native library (csrc/blocks.cu).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from compactor_vllm import _native as N
+
+ACT_SILU, ACT_GELU_TANH = 0, 1
+
+
+def gated_act(x: torch.Tensor, kind: int) -> torch.Tensor:
+    """x [T, 2F] = [gate | up] -> act(gate) * up, [T, F]; kind ACT_SILU or ACT_GELU_TANH (fp32 inside)."""
+    T, F2 = x.shape
+    assert F2 % 2 == 0 and x.stride(1) == 1
+    out = torch.empty((T, F2 // 2), dtype=x.dtype, device=x.device)
+    rc = N.lib().cvllm_gated_act(N.ptr(x), x.stride(0), N.ptr(out), out.stride(0), T, F2 // 2, int(kind),
+                                 N.block_dtype_code(x.dtype), N.stream(x.device))
+    N.check(rc, "cvllm_gated_act")
+    return out
+
+
+def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int, keep: int):
+    """fp32 router logits [T, E] -> (idx int32 [T, top], weights fp32 [T, top]).
+
+    s = softmax(logits); the choice is made on s + correction among the experts of the `keep` best of `groups`
+    neighbour groups (a group's rank is its largest s + correction); the weights are the chosen experts' plain s."""
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    T, E = logits.shape
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    rc = N.lib().cvllm_moe_route(N.ptr(logits), logits.stride(0), N.ptr(correction), T, E, int(top), int(groups),
+                                 int(keep), N.ptr(idx), N.ptr(wts), N.stream(logits.device))
+    N.check(rc, "cvllm_moe_route")
+    return idx, wts
+
+
+class GatedMLP(nn.Module):
+    """down(act(gate x) * up x), gate and up packed in one GEMM."""
+
+    def __init__(self, width: int, ff: int, act: int):
+        super().__init__()
+        self.act = act
+        self.gate_up_proj = nn.Linear(width, 2 * ff, bias=False)
+        self.down_proj = nn.Linear(ff, width, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(gated_act(self.gate_up_proj(x), self.act))
+
+
+class RoutedExperts(nn.Module):
+    """Mixture of `experts` gated experts and `identity` experts that return their input, `top` per token, with
+    group-limited choice, a correction that shifts the choice but not the weights, and an optional shared expert.
+
+    The router runs in fp32.  Tokens are sorted by expert; each expert with tokens runs its two GEMMs on its
+    segment; the combine kernel sums the `top` outputs of every token (identity experts and the shared expert
+    included) in fp32.  Returns fp32 [T, width]."""
+
+    def __init__(self, width: int, ff: int, experts: int, identity: int, top: int, groups: int, keep: int,
+                 shared_ff: int, act: int = ACT_SILU, dtype: torch.dtype | None = None):
+        super().__init__()
+        self.width, self.ff, self.n_real, self.n_identity = width, ff, experts, identity
+        self.top, self.groups, self.keep, self.act = top, groups, keep, act
+        total = experts + identity
+        self.router = nn.Parameter(torch.empty(total, width, dtype=torch.float32))
+        self.correction = nn.Parameter(torch.zeros(total, dtype=torch.float32))
+        self.gate_up = nn.Parameter(torch.empty(experts, 2 * ff, width, dtype=dtype))
+        self.down = nn.Parameter(torch.empty(experts, width, ff, dtype=dtype))
+        self.shared = GatedMLP(width, shared_ff, act) if shared_ff else None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        T, W = x.shape
+        logits = F.linear(x.float(), self.router)
+        idx, wts = route(logits, self.correction, self.top, self.groups, self.keep)
+        shared = self.shared(x) if self.shared is not None else None
+        flat = idx.view(-1).long()
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=self.n_real + self.n_identity)[: self.n_real].tolist()
+        n_rows = sum(counts)
+        pos = torch.empty_like(order, dtype=torch.int32)
+        pos[order] = torch.arange(order.numel(), dtype=torch.int32, device=x.device)
+        ys = torch.empty((max(n_rows, 1), W), dtype=x.dtype, device=x.device)
+        if n_rows:
+            xs = x.index_select(0, order[:n_rows] // self.top)
+            off = 0
+            for e, c in enumerate(counts):
+                if c:
+                    a = gated_act(F.linear(xs[off:off + c], self.gate_up[e]), self.act)
+                    torch.mm(a, self.down[e].t(), out=ys[off:off + c])
+                    off += c
+        out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+        rc = N.lib().cvllm_moe_combine(N.ptr(ys), N.ptr(pos), N.ptr(wts), self.top, N.ptr(idx), self.n_real,
+                                       N.ptr(x), N.ptr(shared), N.ptr(out), T, W, N.block_dtype_code(x.dtype),
+                                       N.stream(x.device))
+        N.check(rc, "cvllm_moe_combine")
+        return out

@@ -37,6 +37,10 @@ _STEP_FIELDS: dict[str, Any] = {
     "STORE_STREAM": None,                # side stream for scoring + store during prefill
     "key_split": None,                   # decode split count fixed at CUDA-graph capture time
     "attention_backend": AttentionBackend.COMPACTOR_TRITON,
+    # mixed steps (portions of prompts beside single decoded tokens; layers/attention.py BiasedChunkAttention)
+    "positions_i32": None,               # int32 [T]: position of every token of the step in its sequence
+    "token_slot": None,                  # int32 [T]: cache slot of every token
+    "seq_start": None,                   # int32 [B]: position of each sequence's first token of this step
 }
 
 

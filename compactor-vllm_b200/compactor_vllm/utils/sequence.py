@@ -27,6 +27,7 @@ class Sequence:
     status: SequenceStatus = SequenceStatus.WAITING
     seq_id: int = field(default_factory=lambda: next(_ids), init=False)
     num_tokens_processed: int = 0
+    num_computed_tokens: int = 0      # tokens whose keys are in the cache (engines that run prompts in portions)
 
     @property
     def num_prompt_tokens(self) -> int:

@@ -1,0 +1,435 @@
+// Attention over the paged cache with a linear distance bias, a chunk mask and an optional softmax sink,
+// for any head size and 32-bit or 16-bit storage.  Three launches per layer:
+//   cvllm_qknorm_store    per-head RMS norm of q and k, k and v written to their cache rows
+//   cvllm_bias_attn_varlen  portions of prompts (any number of new tokens per sequence) against the cache
+//   cvllm_bias_attn_decode  one new token per sequence
+// score(i, j) = scale * q_i . k_j - slope_h * (i - j) for keys j <= i of the same chunk
+// (floor(i / chunk) == floor(j / chunk), chunk 0 = one chunk), positions counted from the start of the
+// sequence; p_j = exp(s_j) / (sink + sum_j exp(s_j)) with sink = 1 (a key of score 0 without a value) or 0.
+// The new tokens' keys are in the cache before the attention launches read it, so both read keys from one place.
+// All arithmetic is fp32; 16-bit storage only rounds q, k, v and the output.
+#include "common.cuh"
+
+namespace cvllm {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+struct PagedKV {
+  const void* k;            // [rows, D]
+  const void* v;            // [rows, Dv]
+  const int32_t* table;     // [slots, G, P]
+  int64_t table_stride_slot, table_stride_head;
+  int page_size;
+};
+
+__device__ __forceinline__ int64_t cache_row(const PagedKV& c, int slot, int g, int pos) {
+  const int page = c.table[slot * c.table_stride_slot + g * c.table_stride_head + pos / c.page_size];
+  return (int64_t)page * c.page_size + pos % c.page_size;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// q / k norm + store.  One CTA per token; its warps take the token's H + 2G head rows in turn.
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) qknorm_store_kernel(
+    const T* __restrict__ qkv, int64_t qkv_stride, const float* __restrict__ q_w, const float* __restrict__ k_w,
+    float eps, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
+    T* __restrict__ k_cache, T* __restrict__ v_cache, PagedKV c, int32_t* __restrict__ bh_lens, int H, int G, int D,
+    int Dv, int reserved_slot) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = token_slot[t];
+  const int pos = positions[t];
+  const T* row = qkv + (int64_t)t * qkv_stride;
+  for (int r = warp; r < H + 2 * G; r += 4) {
+    if (r < H + G) {
+      const bool is_q = r < H;
+      const T* src = row + (int64_t)r * D;  // k heads follow the q heads with the same row size
+      if (!is_q && slot == reserved_slot) continue;
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const float x = to_f<T>(src[d]);
+        ss += x * x;
+      }
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+      const float* w = is_q ? q_w : k_w;
+      T* dst = is_q ? q_out + ((int64_t)t * H + r) * D : k_cache + cache_row(c, slot, r - H, pos) * D;
+      for (int d = lane; d < D; d += 32) {
+        const float x = to_f<T>(src[d]) * inv;
+        dst[d] = from_f<T>(w ? x * w[d] : x);
+      }
+    } else {
+      if (slot == reserved_slot) continue;
+      const int g = r - H - G;
+      const T* src = row + (int64_t)(H + G) * D + (int64_t)g * Dv;
+      T* dst = v_cache + cache_row(c, slot, g, pos) * Dv;
+      for (int d = lane; d < Dv; d += 32) dst[d] = src[d];
+      if (lane == 0 && bh_lens) atomicMax(bh_lens + slot * G + g, pos + 1);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Portions.  CTA = (64-query tile of one sequence's new tokens, query head); 256 threads as 16 x 16: thread
+// (ty, tx) owns query rows 4 ty .. 4 ty + 3, score columns tx + 16 j and output columns tx + 16 c.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int BM = 64;
+
+template <typename T, int BN, int DVC>
+__global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
+    const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_start,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, float scale,
+    T* __restrict__ out, int H, int G, int D, int Dv) {
+  constexpr int NJ = BN / 16;
+  const int b = blockIdx.y, h = blockIdx.z;
+  const int q0 = cu_q[b], n_new = cu_q[b + 1] - q0;
+  const int tile0 = blockIdx.x * BM;
+  if (tile0 >= n_new) return;
+  const int slot = batch_mapping[b];
+  const int g = h / (H / G);
+  const int start = seq_start[b];
+  const int rows = min(BM, n_new - tile0);
+  const int p_first = start + tile0, p_last = p_first + rows - 1;
+  const int lo = chunk > 0 ? (p_first / chunk) * chunk : 0;
+  const float slope = slopes ? slopes[h] : 0.f;
+
+  extern __shared__ float smem[];
+  __shared__ int64_t rix[BN];       // cache row of every key of the tile
+  const int DP = D + 1;
+  float* Qs = smem;                 // [BM][DP]
+  float* Ks = Qs + BM * DP;         // [BN][DP]
+  float* Vs = Ks + BN * DP;         // [BN][Dv]
+  float* Ps = Vs + BN * Dv;         // [BM][BN + 1]
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+
+  for (int i = tid; i < BM * D; i += 256) {
+    const int r = i / D, d = i - r * D;
+    Qs[r * DP + d] = r < rows ? to_f<T>(q[((int64_t)(q0 + tile0 + r) * H + h) * D + d]) : 0.f;
+  }
+  float m[4], l[4], acc[4][DVC];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // with a sink the running maximum starts at the sink's score and the running sum with its term
+    m[i] = sink > 0.f ? 0.f : -INFINITY;
+    l[i] = sink;
+#pragma unroll
+    for (int cc = 0; cc < DVC; ++cc) acc[i][cc] = 0.f;
+  }
+  const T* kc = static_cast<const T*>(c.k);
+  const T* vc = static_cast<const T*>(c.v);
+
+  for (int k0 = lo; k0 <= p_last; k0 += BN) {
+    __syncthreads();  // the previous tile's Ks / Vs / Ps are no longer read
+    const int nk = min(BN, p_last + 1 - k0);
+    if (tid < nk) rix[tid] = cache_row(c, slot, g, k0 + tid);
+    __syncthreads();
+    for (int i = tid; i < BN * D; i += 256) {
+      const int r = i / D, d = i - r * D;
+      Ks[r * DP + d] = r < nk ? to_f<T>(kc[rix[r] * D + d]) : 0.f;
+    }
+    for (int i = tid; i < BN * Dv; i += 256) {
+      const int r = i / Dv, d = i - r * Dv;
+      Vs[i] = r < nk ? to_f<T>(vc[rix[r] * Dv + d]) : 0.f;
+    }
+    __syncthreads();
+    float s[4][NJ];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) s[i][j] = 0.f;
+    for (int d = 0; d < D; ++d) {
+      float qv[4], kv[NJ];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) qv[i] = Qs[(ty * 4 + i) * DP + d];
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) kv[j] = Ks[(tx + 16 * j) * DP + d];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) s[i][j] = fmaf(qv[i], kv[j], s[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty * 4 + i;
+      const int pi = p_first + r;
+      const int lo_i = chunk > 0 ? (pi / chunk) * chunk : 0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const int pj = k0 + tx + 16 * j;
+        const bool ok = r < rows && pj <= pi && pj >= lo_i;
+        s[i][j] = ok ? s[i][j] * scale - slope * (float)(pi - pj) : -INFINITY;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m[i], mx);
+      // m_new == -inf: no key seen so far and none in this tile; everything stays zero
+      const float corr = m_new == -INFINITY ? 1.f : expf(m[i] - m_new);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const float p = s[i][j] == -INFINITY ? 0.f : expf(s[i][j] - m_new);
+        Ps[r * (BN + 1) + tx + 16 * j] = p;
+        sum += p;
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      l[i] = l[i] * corr + sum;
+      m[i] = m_new;
+#pragma unroll
+      for (int cc = 0; cc < DVC; ++cc) acc[i][cc] *= corr;
+    }
+    __syncthreads();
+    for (int j = 0; j < nk; ++j) {
+      float pv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = Ps[(ty * 4 + i) * (BN + 1) + j];
+#pragma unroll
+      for (int cc = 0; cc < DVC; ++cc) {
+        const int col = tx + 16 * cc;
+        if (col < Dv) {
+          const float vv = Vs[j * Dv + col];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i][cc] = fmaf(pv[i], vv, acc[i][cc]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+    const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+#pragma unroll
+    for (int cc = 0; cc < DVC; ++cc) {
+      const int col = tx + 16 * cc;
+      if (col < Dv) out[((int64_t)(q0 + tile0 + r) * H + h) * Dv + col] = from_f<T>(acc[i][cc] * inv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode.  CTA = (sequence, query head), 4 warps; a warp takes 32 keys at a time, one key per lane for the
+// score, one output column per lane (and every 32nd after it) for the value sum; the warps' partial softmax
+// states are merged through shared memory.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kDecWarps = 4;
+constexpr int kDecCols = 8;  // output columns per lane: Dv <= 256
+
+template <typename T>
+__global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
+    const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, float scale,
+    T* __restrict__ out, int H, int G, int D, int Dv, int reserved_slot) {
+  extern __shared__ float smem[];
+  float* qs = smem;                         // [D]
+  float* part = qs + D;                     // [kDecWarps][2 + Dv]
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = batch_mapping[b];
+  T* o = out + ((int64_t)b * H + h) * Dv;
+  if (slot == reserved_slot) {
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) o[d] = from_f<T>(0.f);
+    return;
+  }
+  const int g = h / (H / G);
+  const int pi = positions[b];
+  const int lo = chunk > 0 ? (pi / chunk) * chunk : 0;
+  const float slope = slopes ? slopes[h] : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = to_f<T>(q[((int64_t)b * H + h) * D + d]);
+  __syncthreads();
+  const T* kc = static_cast<const T*>(c.k);
+  const T* vc = static_cast<const T*>(c.v);
+  float m = -INFINITY, l = 0.f, acc[kDecCols];
+#pragma unroll
+  for (int cc = 0; cc < kDecCols; ++cc) acc[cc] = 0.f;
+  for (int k0 = lo + warp * 32; k0 <= pi; k0 += kDecWarps * 32) {
+    const int pj = k0 + lane;
+    const bool ok = pj <= pi;
+    const int64_t row = ok ? cache_row(c, slot, g, pj) : 0;
+    float s = -INFINITY;
+    if (ok) {
+      const T* kr = kc + row * D;
+      float dot = 0.f;
+      for (int d = 0; d < D; ++d) dot = fmaf(qs[d], to_f<T>(kr[d]), dot);
+      s = dot * scale - slope * (float)(pi - pj);
+    }
+    const float m_new = fmaxf(m, warp_max(s));  // lane 0 of the batch is always a live key
+    const float corr = expf(m - m_new);
+    const float p = ok ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+    m = m_new;
+#pragma unroll
+    for (int cc = 0; cc < kDecCols; ++cc) acc[cc] *= corr;
+    const int nk = min(32, pi + 1 - k0);
+    for (int j = 0; j < nk; ++j) {
+      const float pj_w = __shfl_sync(0xffffffffu, p, j);
+      const int64_t rj = __shfl_sync(0xffffffffu, row, j);
+      const T* vr = vc + rj * Dv;
+#pragma unroll
+      for (int cc = 0; cc < kDecCols; ++cc) {
+        const int col = lane + 32 * cc;
+        if (col < Dv) acc[cc] = fmaf(pj_w, to_f<T>(vr[col]), acc[cc]);
+      }
+    }
+  }
+  float* mine = part + warp * (2 + Dv);
+  if (lane == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+  for (int cc = 0; cc < kDecCols; ++cc) {
+    const int col = lane + 32 * cc;
+    if (col < Dv) mine[2 + col] = acc[cc];
+  }
+  __syncthreads();
+  float mm = sink > 0.f ? 0.f : -INFINITY;
+  for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, part[w * (2 + Dv)]);
+  float ll = sink > 0.f ? sink * expf(0.f - mm) : 0.f;
+  float f[kDecWarps];
+  for (int w = 0; w < kDecWarps; ++w) {
+    const float mw = part[w * (2 + Dv)];
+    f[w] = mw == -INFINITY ? 0.f : expf(mw - mm);
+    ll += part[w * (2 + Dv) + 1] * f[w];
+  }
+  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+    float a = 0.f;
+    for (int w = 0; w < kDecWarps; ++w) a += part[w * (2 + Dv) + 2 + d] * f[w];
+    o[d] = from_f<T>(a * inv);
+  }
+}
+
+size_t varlen_smem(int BN, int D, int Dv) {
+  return sizeof(float) * ((size_t)BM * (D + 1) + (size_t)BN * (D + 1) + (size_t)BN * Dv + (size_t)BM * (BN + 1));
+}
+
+template <typename T, int BN, int DVC>
+int launch_varlen(const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start,
+                  const int32_t* batch_mapping, const float* slopes, int chunk, float sink, float scale, void* out,
+                  int B, int max_new, int H, int G, int D, int Dv, cudaStream_t st) {
+  static std::atomic<uint64_t> mask{0};
+  const size_t smem = varlen_smem(BN, D, Dv);
+  auto kern = bias_attn_varlen_kernel<T, BN, DVC>;
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), 226 * 1024, mask));
+  dim3 grid(cdiv(max_new, BM), B, H);
+  kern<<<grid, 256, smem, st>>>(static_cast<const T*>(q), c, cu_q, seq_start, batch_mapping, slopes, chunk, sink,
+                                scale, static_cast<T*>(out), H, G, D, Dv);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+template <typename T, int BN>
+int dispatch_dvc(int dvc, const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start,
+                 const int32_t* bm, const float* slopes, int chunk, float sink, float scale, void* out, int B,
+                 int max_new, int H, int G, int D, int Dv, cudaStream_t st) {
+#define CVLLM_GO(N) \
+  return launch_varlen<T, BN, N>(q, c, cu_q, seq_start, bm, slopes, chunk, sink, scale, out, B, max_new, H, G, D, Dv, st)
+  if (dvc <= 4) CVLLM_GO(4);
+  if (dvc <= 6) CVLLM_GO(6);
+  if (dvc <= 8) CVLLM_GO(8);
+  CVLLM_GO(16);
+#undef CVLLM_GO
+}
+
+}  // namespace
+}  // namespace cvllm
+
+using namespace cvllm;
+
+static int check_dtype(int dtype) { return dtype == CVLLM_BF16 || dtype == CVLLM_F32; }
+
+extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weight, const float* k_weight,
+                                  float eps, const int32_t* positions, const int32_t* token_slot, void* q_out,
+                                  void* k_cache, void* v_cache, const int32_t* page_table, int64_t table_stride_slot,
+                                  int64_t table_stride_head, int page_size, int32_t* bh_lens, int T, int H, int G,
+                                  int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(T >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && page_size > 0);
+  if (T == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(qkv && positions && token_slot && q_out && k_cache && v_cache && page_table && check_dtype(dtype));
+  auto st = static_cast<cudaStream_t>(stream);
+  PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  if (dtype == CVLLM_BF16)
+    qknorm_store_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(qkv), qkv_stride, q_weight, k_weight, eps, positions, token_slot,
+        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+        c, bh_lens, H, G, D, Dv, reserved_slot);
+  else
+    qknorm_store_kernel<float><<<T, 128, 0, st>>>(static_cast<const float*>(qkv), qkv_stride, q_weight, k_weight, eps,
+                                                  positions, token_slot, static_cast<float*>(q_out),
+                                                  static_cast<float*>(k_cache), static_cast<float*>(v_cache), c,
+                                                  bh_lens, H, G, D, Dv, reserved_slot);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cache,
+                                      const int32_t* page_table, int64_t table_stride_slot, int64_t table_stride_head,
+                                      int page_size, const int32_t* cu_seqlens_q, const int32_t* seq_start,
+                                      const int32_t* batch_mapping, const float* slopes, int chunk, int sink,
+                                      float scale, void* out, int B, int max_new, int H, int G, int D, int Dv,
+                                      int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
+  if (B == 0 || max_new == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && cu_seqlens_q && seq_start && batch_mapping && out &&
+                  check_dtype(dtype) && page_size > 0);
+  CVLLM_CHECK_SUPPORTED(Dv <= 256 && B <= 65535 && H <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  const int dvc = cdiv(Dv, 16);
+  const float fs = sink ? 1.f : 0.f;
+  const size_t cap = 226 * 1024;  // + the static row-index array
+  int bn = 64;
+  while (bn > 32 && varlen_smem(bn, D, Dv) > cap) bn >>= 1;
+  CVLLM_CHECK_SUPPORTED(varlen_smem(bn, D, Dv) <= cap);
+#define CVLLM_GO(T, BN) \
+  return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B, \
+                             max_new, H, G, D, Dv, st)
+  if (dtype == CVLLM_BF16) {
+    if (bn == 64) CVLLM_GO(__nv_bfloat16, 64);
+    CVLLM_GO(__nv_bfloat16, 32);
+  }
+  if (bn == 64) CVLLM_GO(float, 64);
+  CVLLM_GO(float, 32);
+#undef CVLLM_GO
+}
+
+extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cache,
+                                      const int32_t* page_table, int64_t table_stride_slot, int64_t table_stride_head,
+                                      int page_size, const int32_t* positions, const int32_t* batch_mapping,
+                                      const float* slopes, int chunk, int sink, float scale, void* out, int B, int H,
+                                      int G, int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
+  if (B == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && positions && batch_mapping && out && check_dtype(dtype) &&
+                  page_size > 0);
+  CVLLM_CHECK_SUPPORTED(Dv <= 32 * kDecCols && H <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  const size_t smem = sizeof(float) * ((size_t)D + (size_t)kDecWarps * (2 + Dv));
+  CVLLM_CHECK_SUPPORTED(smem <= 48 * 1024);
+  dim3 grid(B, H);
+  if (dtype == CVLLM_BF16)
+    bias_attn_decode_kernel<__nv_bfloat16><<<grid, kDecWarps * 32, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, scale,
+        static_cast<__nv_bfloat16*>(out), H, G, D, Dv, reserved_slot);
+  else
+    bias_attn_decode_kernel<float><<<grid, kDecWarps * 32, smem, st>>>(
+        static_cast<const float*>(q), c, positions, batch_mapping, slopes, chunk, sink ? 1.f : 0.f, scale,
+        static_cast<float*>(out), H, G, D, Dv, reserved_slot);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}

@@ -1,0 +1,297 @@
+// Model blocks around the attention path that keep a 32-bit residual stream: sandwich RMS norm
+// (post-norm of a branch added into the residual, fused with the pre-norm of the next branch), gated
+// activations over packed [gate | up] rows, and a softmax router with group-limited top-k choice.
+// Every kernel takes 32-bit or 16-bit activations; norm statistics, softmax and the residual are always 32-bit.
+#include "common.cuh"
+
+namespace cvllm {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+constexpr int kThreads = 256;
+
+// sum over the CTA; every thread gets the result.  `red` holds one float per warp.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // red may still be read from an earlier call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < (int)(blockDim.x >> 5)) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+// One CTA per row.  row (dynamic shared memory) holds the row in fp32 between the passes.
+//   y != NULL:      resid += y / sqrt(mean(y^2) + eps) * w_post
+//   w_pre != NULL:  out = resid / sqrt(mean(resid^2) + eps) * w_pre
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(kThreads) sandwich_norm_kernel(
+    const TY* __restrict__ y, int64_t y_stride, const float* __restrict__ w_post, float* __restrict__ resid,
+    int64_t r_stride, const float* __restrict__ w_pre, TO* __restrict__ out, int64_t o_stride, int width,
+    float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[kThreads / 32];
+  const int64_t r = blockIdx.x;
+  float* res = resid + r * r_stride;
+  if (y != nullptr) {
+    const TY* yr = y + r * y_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+      const float v = to_f<TY>(yr[i]);
+      row[i] = v;
+      ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += kThreads) {
+      const float v = res[i] + row[i] * inv * w_post[i];
+      res[i] = v;
+      row[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += kThreads) row[i] = res[i];
+  }
+  if (w_pre == nullptr) return;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += kThreads) ss += row[i] * row[i];
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  TO* o = out + r * o_stride;
+  for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i] * inv * w_pre[i]);
+}
+
+__device__ __forceinline__ float act_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float act_gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// out[t, f] = act(x[t, f]) * x[t, F + f]
+template <typename T, int KIND>
+__global__ void gated_act_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ out,
+                                 int64_t o_stride, int64_t rows, int F) {
+  const int64_t total = rows * (int64_t)F;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / F;
+    const int f = (int)(i - t * F);
+    const float g = to_f<T>(x[t * x_stride + f]);
+    const float u = to_f<T>(x[t * x_stride + F + f]);
+    const float a = KIND == 0 ? act_silu(g) : act_gelu_tanh(g);
+    out[t * o_stride + f] = from_f<T>(a * u);
+  }
+}
+
+// Lowest index among the largest values of v[0..n) (lanes strided), then the same answer in every lane.
+__device__ __forceinline__ int warp_argmax(const float* v, int n, float* best_out) {
+  const int lane = threadIdx.x & 31;
+  float best = -INFINITY;
+  int at = 0x7fffffff;
+  for (int e = lane; e < n; e += 32) {
+    const float c = v[e];
+    if (c > best || (c == best && e < at)) { best = c; at = e; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+    if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+  }
+  *best_out = best;
+  return at;
+}
+
+constexpr int kRouteWarps = 4;
+
+// One warp per token.  s = softmax(logits); choice = s + correction; experts outside the `keep` groups with
+// the largest group maximum of choice are struck; the `top` largest remaining choices are taken, each with
+// its plain s as weight.  Shared memory per warp: s[E], choice[E], group maxima[groups].
+__global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
+    const float* __restrict__ logits, int64_t l_stride, const float* __restrict__ correction, int T, int E,
+    int top, int groups, int keep, int32_t* __restrict__ idx, float* __restrict__ wts) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= T) return;
+  float* s = sm + (size_t)warp * (2 * E + groups);
+  float* c = s + E;
+  float* gm = c + E;
+  const float* z = logits + (int64_t)t * l_stride;
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float p = expf(z[e] - m);
+    s[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  for (int e = lane; e < E; e += 32) {
+    const float p = s[e] / sum;
+    s[e] = p;
+    c[e] = correction ? p + correction[e] : p;
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int size = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float b = -INFINITY;
+      for (int e = g * size; e < (g + 1) * size; ++e) b = fmaxf(b, c[e]);
+      gm[g] = b;
+    }
+    __syncwarp();
+    // a kept group's maximum is overwritten with NaN as its mark; experts of unmarked groups are struck afterwards
+    for (int r = 0; r < keep; ++r) {
+      float b;
+      const int g = warp_argmax(gm, groups, &b);
+      __syncwarp();
+      if (lane == 0) gm[g] = NAN;  // NaN never wins a '>' or '==' comparison again
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!isnan(gm[e / size])) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int r = 0; r < top; ++r) {
+    float b;
+    const int e = warp_argmax(c, E, &b);
+    __syncwarp();
+    if (lane == 0) {
+      idx[(int64_t)t * top + r] = e;
+      wts[(int64_t)t * top + r] = s[e];
+      c[e] = NAN;
+    }
+    __syncwarp();
+  }
+}
+
+// out[t, :] = sum_r w[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :])  (+ shared[t, :]),  fp32 sums.
+// pos maps a (token, choice) pair to its row of y (the pairs sorted by expert); NULL = the pair's own index.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ pos,
+                                   const float* __restrict__ w, int top,
+                                   const int32_t* __restrict__ idx, int n_real, const T* __restrict__ h,
+                                   const T* __restrict__ shared, float* __restrict__ out, int64_t rows, int width) {
+  const int64_t total = rows * (int64_t)width;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / width;
+    const int c = (int)(i - t * width);
+    float acc = shared ? to_f<T>(shared[i]) : 0.f;
+    for (int r = 0; r < top; ++r) {
+      const float wr = w[t * top + r];
+      if (idx[t * top + r] >= n_real)
+        acc += wr * to_f<T>(h[i]);
+      else
+        acc += wr * to_f<T>(y[(int64_t)(pos ? pos[t * top + r] : t * top + r) * width + c]);
+    }
+    out[i] = acc;
+  }
+}
+
+}  // namespace
+}  // namespace cvllm
+
+using namespace cvllm;
+
+extern "C" int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype, const float* w_post, float* resid,
+                                   int64_t r_stride, const float* w_pre, void* out, int64_t o_stride,
+                                   int out_dtype, int rows, int width, float eps, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(rows >= 0 && width > 0 && resid);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG((y == nullptr) == (w_post == nullptr));
+  CVLLM_CHECK_ARG((w_pre == nullptr) == (out == nullptr));
+  CVLLM_CHECK_ARG(y == nullptr || y_dtype == CVLLM_BF16 || y_dtype == CVLLM_F32);
+  CVLLM_CHECK_ARG(out == nullptr || out_dtype == CVLLM_BF16 || out_dtype == CVLLM_F32);
+  CVLLM_CHECK_SUPPORTED(width <= 12288);
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)width * sizeof(float);
+  const bool yb = y_dtype == CVLLM_BF16, ob = out_dtype == CVLLM_BF16;
+#define CVLLM_SANDWICH(TY, TO)                                                                                 \
+  sandwich_norm_kernel<TY, TO><<<rows, kThreads, smem, st>>>(static_cast<const TY*>(y), y_stride, w_post,      \
+                                                             resid, r_stride, w_pre, static_cast<TO*>(out),    \
+                                                             o_stride, width, eps)
+  if (yb && ob) CVLLM_SANDWICH(__nv_bfloat16, __nv_bfloat16);
+  else if (yb) CVLLM_SANDWICH(__nv_bfloat16, float);
+  else if (ob) CVLLM_SANDWICH(float, __nv_bfloat16);
+  else CVLLM_SANDWICH(float, float);
+#undef CVLLM_SANDWICH
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F,
+                               int kind, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(rows >= 0 && F > 0 && (kind == 0 || kind == 1));
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(x && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  auto st = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * (int64_t)F;
+  const int grid = (int)((total + 255) / 256 < (int64_t)sm_count() * 16 ? (total + 255) / 256 : (int64_t)sm_count() * 16);
+#define CVLLM_GATED(T, K)                                                                                      \
+  gated_act_kernel<T, K><<<grid, 256, 0, st>>>(static_cast<const T*>(x), x_stride, static_cast<T*>(out),       \
+                                               o_stride, rows, F)
+  if (dtype == CVLLM_BF16) {
+    if (kind == 0) CVLLM_GATED(__nv_bfloat16, 0); else CVLLM_GATED(__nv_bfloat16, 1);
+  } else {
+    if (kind == 0) CVLLM_GATED(float, 0); else CVLLM_GATED(float, 1);
+  }
+#undef CVLLM_GATED
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_moe_route(const float* logits, int64_t l_stride, const float* correction, int T, int E, int top,
+                               int groups, int keep, int32_t* idx, float* wts, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(T >= 0 && E > 0 && top > 0 && top <= E && groups > 0 && keep > 0 && keep <= groups);
+  if (T == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(logits && idx && wts && E % groups == 0 && keep * (E / groups) >= top);
+  CVLLM_CHECK_SUPPORTED(E <= 2048);
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)kRouteWarps * (2 * E + groups) * sizeof(float);
+  static std::atomic<uint64_t> mask{0};
+  if (smem > 48 * 1024)
+    CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(route_kernel), (int)smem, mask));
+  route_kernel<<<cdiv(T, kRouteWarps), kRouteWarps * 32, smem, st>>>(logits, l_stride, correction, T, E, top,
+                                                                    groups, keep, idx, wts);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_moe_combine(const void* y, const int32_t* pos, const float* w, int top, const int32_t* idx, int n_real,
+                                 const void* h, const void* shared, float* out, int64_t rows, int width, int dtype,
+                                 cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(rows >= 0 && width > 0 && top > 0);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(y && w && idx && h && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  auto st = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * (int64_t)width;
+  const int grid = (int)((total + 255) / 256 < (int64_t)sm_count() * 16 ? (total + 255) / 256 : (int64_t)sm_count() * 16);
+  if (dtype == CVLLM_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(y), pos, w, top, idx, n_real, static_cast<const __nv_bfloat16*>(h),
+        static_cast<const __nv_bfloat16*>(shared), out, rows, width);
+  else
+    moe_combine_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(y), pos, w, top, idx, n_real,
+                                                    static_cast<const float*>(h), static_cast<const float*>(shared),
+                                                    out, rows, width);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}

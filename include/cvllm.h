@@ -35,7 +35,8 @@ extern "C" {
 
 #define CVLLM_ABI_VERSION 1
 
-enum { CVLLM_F16 = 0, CVLLM_BF16 = 1 };
+/* CVLLM_F32: 32-bit storage; only the entry points of the "model blocks" and "biased attention" sections take it. */
+enum { CVLLM_F16 = 0, CVLLM_BF16 = 1, CVLLM_F32 = 3 };
 
 enum {
   CVLLM_OK = 0,
@@ -394,6 +395,72 @@ int cvllm_selftest_eig(const float* gram, double* lam_out, double* vec_out, floa
  * --------------------------------------------------------------------- */
 int cvllm_selftest_umma(const void* a, const void* b, float* d, int mode,
                         uint32_t lbo, uint32_t sbo, int dtype, cvllm_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Model blocks with a 32-bit residual stream (csrc/blocks.cu).  dtype arguments: CVLLM_BF16 or CVLLM_F32.
+ * Norm weights, router logits, routing weights and the residual are fp32.
+ * --------------------------------------------------------------------- */
+
+/* Sandwich RMS norm, one launch per residual update, rows independent:
+ *   y != NULL:      resid += y / sqrt(mean(y^2) + eps) * w_post        (y [rows, width] of y_dtype)
+ *   w_pre != NULL:  out = resid / sqrt(mean(resid^2) + eps) * w_pre     (out [rows, width] of out_dtype)
+ * y and w_post come together, w_pre and out come together.  width <= 12288.  Strides in elements. */
+int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype, const float* w_post, float* resid,
+                        int64_t r_stride, const float* w_pre, void* out, int64_t o_stride, int out_dtype,
+                        int rows, int width, float eps, cvllm_stream_t stream);
+
+/* out[t, f] = act(x[t, f]) * x[t, F + f] for packed [gate | up] rows; kind 0 = silu, 1 = gelu (tanh form). */
+int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F, int kind,
+                    int dtype, cvllm_stream_t stream);
+
+/* Router: s = softmax(logits[t, :E]); choice = s + correction (NULL = none).  The E outputs form `groups` equal
+ * runs of neighbours; only the `keep` groups with the largest maximum of choice stay eligible; of those the `top`
+ * largest choices are taken (ties: the lower index).  idx int32 [T, top], wts fp32 [T, top] = the plain s of the
+ * chosen outputs, not renormalised.  E <= 2048, E % groups == 0, keep * E / groups >= top. */
+int cvllm_moe_route(const float* logits, int64_t l_stride, const float* correction, int T, int E, int top,
+                    int groups, int keep, int32_t* idx, float* wts, cvllm_stream_t stream);
+
+/* out[t, :] = sum_r wts[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :]) + shared[t, :]
+ * in fp32.  y holds one row per (token, choice) pair with a real expert, at the row pos gives (NULL: the pair's
+ * own index); outputs idx >= n_real are identity experts (their output is the input h).  shared may be NULL. */
+int cvllm_moe_combine(const void* y, const int32_t* pos, const float* wts, int top, const int32_t* idx, int n_real,
+                      const void* h, const void* shared, float* out, int64_t rows, int width, int dtype,
+                      cvllm_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Biased attention over the paged cache (csrc/bias_attn.cu): any head size, CVLLM_BF16 or CVLLM_F32 storage,
+ * fp32 arithmetic.  score(i, j) = scale * q_i . k_j - slopes[h] * (i - j) for j <= i with
+ * floor(i / chunk) == floor(j / chunk) (chunk 0: no chunking; slopes NULL: no bias);
+ * p_j = exp(s_j) / (sink + sum exp(s_j)), sink 0 or 1.  Positions count from the start of each sequence.
+ * The cache is the one of the store path: k_cache [rows, D], v_cache [rows, Dv], page_table[slot, head, page]
+ * with the two strides given, page_size rows per page.
+ * --------------------------------------------------------------------- */
+
+/* qkv [T, H*D + G*D + G*Dv] packed rows -> q_out [T, H, D] (per-head RMS norm, weight q_weight [D] or NULL),
+ * keys (same norm with k_weight) and values written to the cache row of (token_slot[t], head, positions[t]);
+ * bh_lens[slot, head] (may be NULL) is raised to positions[t] + 1.  Tokens of reserved_slot store nothing. */
+int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weight, const float* k_weight,
+                       float eps, const int32_t* positions, const int32_t* token_slot, void* q_out,
+                       void* k_cache, void* v_cache, const int32_t* page_table, int64_t table_stride_slot,
+                       int64_t table_stride_head, int page_size, int32_t* bh_lens, int T, int H, int G, int D,
+                       int Dv, int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* Portions: sequence b brings tokens cu_seqlens_q[b] .. cu_seqlens_q[b+1]-1 at positions seq_start[b] + 0, 1, ...;
+ * all their keys (and every earlier one) are in the cache of slot batch_mapping[b].  out [T, H, Dv].
+ * max_new = the largest number of new tokens of one sequence.  Dv <= 256. */
+int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+                           int64_t table_stride_slot, int64_t table_stride_head, int page_size,
+                           const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* batch_mapping,
+                           const float* slopes, int chunk, int sink, float scale, void* out, int B, int max_new,
+                           int H, int G, int D, int Dv, int dtype, cvllm_stream_t stream);
+
+/* Decode: one query per sequence at position positions[b] (its key is in the cache already).  q [B, H, D],
+ * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 256. */
+int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
+                           int64_t table_stride_slot, int64_t table_stride_head, int page_size,
+                           const int32_t* positions, const int32_t* batch_mapping, const float* slopes, int chunk,
+                           int sink, float scale, void* out, int B, int H, int G, int D, int Dv, int reserved_slot,
+                           int dtype, cvllm_stream_t stream);
 
 #ifdef __cplusplus
 }
