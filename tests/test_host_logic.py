@@ -57,9 +57,10 @@ def test_context_records_are_dataclasses():
     from compactor_vllm.utils.context import CompressionContext, Context, get_context, reset_context, set_context
 
     names = [f.name for f in dataclasses.fields(Context)]
+    # the reference's fields in the reference's order, then the ones mixed steps add
     assert names == ["is_prefill", "do_compression", "cu_seqlens_q", "cu_seqlens_k", "max_seqlen_q", "max_seqlen_k",
                      "batch_mapping", "max_bh_len", "compression_context", "STORE_STREAM", "key_split",
-                     "attention_backend"]
+                     "attention_backend", "positions_i32", "token_slot", "seq_start"]
     assert [f.name for f in dataclasses.fields(CompressionContext)] == [
         "compression_method", "compression_chunk_size", "batch_tokens_to_retain", "max_tokens_to_retain",
         "context_lens", "PHI", "protected_first_tokens", "protected_last_tokens"]
