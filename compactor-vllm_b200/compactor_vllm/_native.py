@@ -81,6 +81,7 @@ _SIGNATURES = {
     "cvllm_gated_act": (_i, [_p, _i64, _p, _i64, _i64, _i, _i, _i, _p]),
     "cvllm_moe_route": (_i, [_p, _i64, _p, _i, _i, _i, _i, _i, _p, _p, _p]),
     "cvllm_moe_combine": (_i, [_p, _p, _p, _i, _p, _i, _p, _p, _p, _i64, _i, _i, _p]),
+    "cvllm_expert_gemv": (_i, [_p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
     "cvllm_qknorm_store": (_i, [_p, _i64, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
                                 _i, _i, _i, _i, _i, _i, _i, _p]),
     "cvllm_bias_attn_varlen": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _f, _p,

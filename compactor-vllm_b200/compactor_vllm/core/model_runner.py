@@ -107,6 +107,7 @@ class ModelRunner:
         self.max_batched_tokens = int(max_batched_tokens or config.max_model_len)
         self.eos = config.eos
         self._graphs: dict = {}
+        self._step_graphs: dict = {}
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "graph_replays": 0, "bytes_reclaimed": 0, "steps": 0}
 
     # ------------------------------------------------------------------ prefill
@@ -265,6 +266,13 @@ class ModelRunner:
         if not ok:
             raise KVCacheExhausted(f"no room for a step of {sum(lens)} tokens ({self.kv.num_free_tokens} tokens free)")
         T = sum(lens)
+        if max(lens) == 1 and not self.config.enforce_eager:
+            logits = self._graph_decode_step(entries, starts, rows)
+            for s, _ in entries:
+                s.num_computed_tokens += 1
+            self.stats["steps"] += 1
+            self.stats["graph_replays"] += 1
+            return logits
         # one host->device copy for all the step's index vectors
         pos = [p for st, n in zip(starts, lens) for p in range(st, st + n)]
         slot_of = [self.kv.seq_id_to_batch[s.seq_id] for s, _ in entries]
@@ -288,6 +296,48 @@ class ModelRunner:
         self.stats["steps"] += 1
         self.stats["prefill_tokens"] += sum(n for n in lens if n > 1)
         return logits
+
+    def _graph_decode_step(self, entries, starts, rows) -> torch.Tensor:
+        """A step of single tokens as a CUDA-graph replay (one graph per padded batch size; padding rows sit on the
+        reserved slot, store nothing and attend to nothing).  The graph holds the whole forward pass and the logits of
+        every row; ids, positions and slots are copied into its static buffer before the replay."""
+        dev = self.device
+        B = len(entries)
+        bs = _pad_batch(B)
+        g = self._step_graphs.get(bs)
+        if g is None:
+            st = {"packed": torch.zeros(3 * bs, dtype=torch.int32, device=dev)}
+            st["packed"][2 * bs:] = RESERVED_BATCH
+
+            def forward():
+                pk = st["packed"]
+                ids, pos, slots = pk[:bs].long(), pk[bs:2 * bs], pk[2 * bs:]
+                set_context(is_prefill=False, batch_mapping=slots, positions_i32=pos, token_slot=slots,
+                            max_seqlen_q=1)
+                hidden = self.model(ids, pos.long())
+                out = self.model.lm_head(hidden)
+                reset_context()
+                return out
+
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                forward()                      # warm-up on the reserved slot: workspaces, library handles
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    st["logits"] = forward()
+            torch.cuda.current_stream().wait_stream(side)
+            g = self._step_graphs[bs] = (graph, st)
+        graph, st = g
+        pad = bs - B
+        slot_of = [self.kv.seq_id_to_batch[s.seq_id] for s, _ in entries]
+        host = torch.tensor([toks[0] for _, toks in entries] + [0] * pad + list(starts) + [0] * pad
+                            + slot_of + [RESERVED_BATCH] * pad, dtype=torch.int32).pin_memory()
+        st["packed"].copy_(host, non_blocking=True)
+        graph.replay()
+        pick = list(range(B)) if rows is None else list(rows)
+        return st["logits"].index_select(0, torch.tensor(pick, dtype=torch.int64, device=dev))
 
     def release(self, seqs: Seq[Sequence]) -> None:
         """Give back the slots and pages of finished sequences."""

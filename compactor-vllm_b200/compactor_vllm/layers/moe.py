@@ -10,6 +10,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from compactor_vllm import _native as N
+from compactor_vllm.utils.context import get_context
 
 ACT_SILU, ACT_GELU_TANH = 0, 1
 
@@ -57,9 +58,14 @@ class RoutedExperts(nn.Module):
     """Mixture of `experts` gated experts and `identity` experts that return their input, `top` per token, with
     group-limited choice, a correction that shifts the choice but not the weights, and an optional shared expert.
 
-    The router runs in fp32.  Tokens are sorted by expert; each expert with tokens runs its two GEMMs on its
-    segment; the combine kernel sums the `top` outputs of every token (identity experts and the shared expert
-    included) in fp32.  Returns fp32 [T, width]."""
+    The router runs in fp32.  Portions: tokens are sorted by expert, each expert with tokens runs its two GEMMs on
+    its segment (the per-expert counts cross to the host once per layer).  Few tokens (decode steps, and any step of
+    at most `SMALL_STEP` tokens): `cvllm_expert_gemv` reads each chosen expert's rows straight from the routing
+    indices on the device, so the step has no host round trip and can be captured in a CUDA graph.  Either way the
+    combine kernel sums the `top` outputs of every token (identity experts and the shared expert included) in fp32.
+    Returns fp32 [T, width]."""
+
+    SMALL_STEP = 8
 
     def __init__(self, width: int, ff: int, experts: int, identity: int, top: int, groups: int, keep: int,
                  shared_ff: int, act: int = ACT_SILU, dtype: torch.dtype | None = None):
@@ -78,6 +84,19 @@ class RoutedExperts(nn.Module):
         logits = F.linear(x.float(), self.router)
         idx, wts = route(logits, self.correction, self.top, self.groups, self.keep)
         shared = self.shared(x) if self.shared is not None else None
+        out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+        lib, code, st = N.lib(), N.block_dtype_code(x.dtype), N.stream(x.device)
+        if not get_context().is_prefill or T <= self.SMALL_STEP:
+            pairs = T * self.top
+            a = torch.empty((pairs, self.ff), dtype=x.dtype, device=x.device)
+            ys = torch.empty((pairs, W), dtype=x.dtype, device=x.device)
+            N.check(lib.cvllm_expert_gemv(N.ptr(x), self.top, N.ptr(self.gate_up), N.ptr(idx), self.n_real, N.ptr(a),
+                                          pairs, self.ff, W, self.act, code, st), "cvllm_expert_gemv")
+            N.check(lib.cvllm_expert_gemv(N.ptr(a), 1, N.ptr(self.down), N.ptr(idx), self.n_real, N.ptr(ys),
+                                          pairs, W, self.ff, -1, code, st), "cvllm_expert_gemv")
+            N.check(lib.cvllm_moe_combine(N.ptr(ys), None, N.ptr(wts), self.top, N.ptr(idx), self.n_real, N.ptr(x),
+                                          N.ptr(shared), N.ptr(out), T, W, code, st), "cvllm_moe_combine")
+            return out
         flat = idx.view(-1).long()
         order = torch.argsort(flat, stable=True)
         counts = torch.bincount(flat, minlength=self.n_real + self.n_identity)[: self.n_real].tolist()
@@ -93,9 +112,6 @@ class RoutedExperts(nn.Module):
                     a = gated_act(F.linear(xs[off:off + c], self.gate_up[e]), self.act)
                     torch.mm(a, self.down[e].t(), out=ys[off:off + c])
                     off += c
-        out = torch.empty((T, W), dtype=torch.float32, device=x.device)
-        rc = N.lib().cvllm_moe_combine(N.ptr(ys), N.ptr(pos), N.ptr(wts), self.top, N.ptr(idx), self.n_real,
-                                       N.ptr(x), N.ptr(shared), N.ptr(out), T, W, N.block_dtype_code(x.dtype),
-                                       N.stream(x.device))
-        N.check(rc, "cvllm_moe_combine")
+        N.check(lib.cvllm_moe_combine(N.ptr(ys), N.ptr(pos), N.ptr(wts), self.top, N.ptr(idx), self.n_real, N.ptr(x),
+                                      N.ptr(shared), N.ptr(out), T, W, code, st), "cvllm_moe_combine")
         return out

@@ -43,7 +43,7 @@ def main(argv=None) -> int:
     # a request's share of --max-tokens is rounded to 64; with larger pages each live request may need one more
     pages = -(-a.max_tokens // ps) + (MAX_LIVE if ps > 64 else 0)
     cfg = LLMConfig(model=a.model, path=a.model, dtype=a.dtype, max_num_seqs=MAX_LIVE, kvcache_page_size=ps,
-                    max_model_len=pages * ps, enforce_eager=True)
+                    max_model_len=pages * ps)
     runner = ModelRunner(cfg, num_pages=pages, device_allocator=False)
     if not runner.mixed_steps:
         print(f"model type {cfg.hf_config.model_type!r} cannot run portions of prompts", file=sys.stderr)

@@ -206,6 +206,42 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __res
   }
 }
 
+
+// Expert products for a few tokens (decode): one warp per (pair, output), pair = (token, choice).
+//   GATED:  out[p, f] = act(W[e, f, :] . x) * W[e, F + f, :] . x        (W [E, 2F, K])
+//   else:   out[p, n] = W[e, n, :] . x                                   (W [E, N, K])
+// with e = idx[p] and x = row p / x_div of xs.  Pairs whose expert is >= n_real (identity experts) are skipped.
+// No host knowledge of the routing is needed, so the step can be replayed from a CUDA graph.
+template <typename T, bool GATED, int KIND>
+__global__ void __launch_bounds__(256) expert_gemv_kernel(const T* __restrict__ xs, int x_div,
+                                                          const T* __restrict__ w, const int32_t* __restrict__ idx,
+                                                          int n_real, T* __restrict__ out, int N, int K) {
+  const int p = blockIdx.y;
+  const int e = idx[p];
+  if (e >= n_real) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= N) return;
+  const T* x = xs + (int64_t)(p / x_div) * K;
+  const int rows = GATED ? 2 * N : N;
+  const T* w0 = w + ((int64_t)e * rows + n) * K;
+  float a = 0.f, b = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float xv = to_f<T>(x[k]);
+    a = fmaf(to_f<T>(w0[k]), xv, a);
+    if (GATED) b = fmaf(to_f<T>(w0[(int64_t)N * K + k]), xv, b);
+  }
+  a = warp_sum(a);
+  if (GATED) {
+    b = warp_sum(b);
+    // the library GEMM path rounds gate and up to the storage type before the activation; do the same
+    a = to_f<T>(from_f<T>(a));
+    b = to_f<T>(from_f<T>(b));
+    a = (KIND == 0 ? act_silu(a) : act_gelu_tanh(a)) * b;
+  }
+  if (lane == 0) out[(int64_t)p * N + n] = from_f<T>(a);
+}
+
 }  // namespace
 }  // namespace cvllm
 
@@ -292,6 +328,31 @@ extern "C" int cvllm_moe_combine(const void* y, const int32_t* pos, const float*
     moe_combine_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(y), pos, w, top, idx, n_real,
                                                     static_cast<const float*>(h), static_cast<const float*>(shared),
                                                     out, rows, width);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const int32_t* idx, int n_real, void* out,
+                                 int pairs, int N, int K, int gated_kind, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(pairs >= 0 && N > 0 && K > 0 && x_div > 0 && gated_kind >= -1 && gated_kind <= 1);
+  if (pairs == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(xs && w && idx && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
+  CVLLM_CHECK_SUPPORTED(pairs <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  dim3 grid(cdiv(N, 8), pairs);
+#define CVLLM_GEMV(T, G, KD)                                                                                   \
+  expert_gemv_kernel<T, G, KD><<<grid, 256, 0, st>>>(static_cast<const T*>(xs), x_div, static_cast<const T*>(w), \
+                                                     idx, n_real, static_cast<T*>(out), N, K)
+  if (dtype == CVLLM_BF16) {
+    if (gated_kind < 0) CVLLM_GEMV(__nv_bfloat16, false, 0);
+    else if (gated_kind == 0) CVLLM_GEMV(__nv_bfloat16, true, 0);
+    else CVLLM_GEMV(__nv_bfloat16, true, 1);
+  } else {
+    if (gated_kind < 0) CVLLM_GEMV(float, false, 0);
+    else if (gated_kind == 0) CVLLM_GEMV(float, true, 0);
+    else CVLLM_GEMV(float, true, 1);
+  }
+#undef CVLLM_GEMV
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }

@@ -427,6 +427,14 @@ int cvllm_moe_combine(const void* y, const int32_t* pos, const float* wts, int t
                       const void* h, const void* shared, float* out, int64_t rows, int width, int dtype,
                       cvllm_stream_t stream);
 
+/* Expert products for a few tokens without host knowledge of the routing (decode, CUDA graphs): one row per
+ * (token, choice) pair p with expert e = idx[p] and input row p / x_div of xs [.., K]:
+ *   gated_kind 0 | 1:  out[p, f] = act(w[e, f, :] . x) * w[e, N + f, :] . x,  w [E, 2N, K], act = silu | gelu (tanh)
+ *   gated_kind -1:     out[p, n] = w[e, n, :] . x,                            w [E, N, K]
+ * Pairs with e >= n_real are left untouched.  out [pairs, N]. */
+int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const int32_t* idx, int n_real, void* out,
+                      int pairs, int N, int K, int gated_kind, int dtype, cvllm_stream_t stream);
+
 /* ------------------------------------------------------------------------
  * Biased attention over the paged cache (csrc/bias_attn.cu): any head size, CVLLM_BF16 or CVLLM_F32 storage,
  * fp32 arithmetic.  score(i, j) = scale * q_i . k_j - slopes[h] * (i - j) for j <= i with

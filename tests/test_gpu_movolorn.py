@@ -46,14 +46,14 @@ def config_b(chunk=256, heads=2, kv_heads=1, dim=32):
 
 
 def make_runner(cfg_json, dtype="float32", pages=24, page_size=16, max_seqs=4, seed=0, max_batched_tokens=None,
-                device_allocator=False):
+                device_allocator=False, eager=True):
     from compactor_vllm.config.engine_config import LLMConfig
     from compactor_vllm.config.model_config import MovolornConfig
     from compactor_vllm.core.model_runner import ModelRunner
 
     hf = MovolornConfig.from_json(cfg_json)
     cfg = LLMConfig(model="synthetic", hf_config=hf, dtype=dtype, max_num_seqs=max_seqs, kvcache_page_size=page_size,
-                    max_model_len=pages * page_size, enforce_eager=True)
+                    max_model_len=pages * page_size, enforce_eager=eager)
     return ModelRunner(cfg, num_pages=pages, seed=seed, device_allocator=device_allocator,
                        max_batched_tokens=max_batched_tokens)
 
@@ -278,10 +278,12 @@ def test_whole_prompt_portions_and_token_by_token(dtype):
             assert rel_err(got, whole.cpu()) < 1e-5, sizes
 
 
-def test_long_decoding_over_pages_and_chunks():
+@pytest.mark.parametrize("eager", [True, False])
+def test_long_decoding_over_pages_and_chunks(eager):
+    """eager=False: single-token steps are CUDA-graph replays, the routed experts run without a host round trip."""
     from oracle import movolorn as O
 
-    r = make_runner(config_a(), "float32", pages=16, page_size=16)
+    r = make_runner(config_a(), "float32", pages=16, page_size=16, eager=eager)
     om = oracle_model(r.model)
     toks = tokens(200, 97, 6)
     want = O.forward(om, toks)
@@ -291,6 +293,31 @@ def test_long_decoding_over_pages_and_chunks():
         out.append(feed(r, seq, [t]))
     r.release([seq])
     assert rel_err(torch.cat(out), want) < TOL["float32"]
+    assert (r.stats["graph_replays"] > 0) == (not eager)
+
+
+def test_graph_decode_batches_with_padding_rows():
+    """Three decoding requests (padded to four rows in the graph) of unequal lengths, one of which ends early."""
+    from oracle import movolorn as O
+
+    r = make_runner(config_a(), "float32", pages=20, page_size=16, eager=False)
+    om = oracle_model(r.model)
+    reqs = [tokens(n, 97, 40 + i) for i, n in enumerate((30, 12, 21))]
+    want = [O.forward(om, t) for t in reqs]
+    seqs = [new_seq() for _ in reqs]
+    got = [[feed(r, s, t[:4])] for s, t in zip(seqs, reqs)]
+    for k in range(4, 30):
+        live = [i for i, t in enumerate(reqs) if k < len(t)]
+        for i in live:
+            seqs[i].prompt_token_ids.append(reqs[i][k])
+        logits = r.run_step([(seqs[i], [reqs[i][k]]) for i in live])
+        for j, i in enumerate(live):
+            got[i].append(logits[j:j + 1])
+        done = [i for i in live if k == len(reqs[i]) - 1]
+        r.release([seqs[i] for i in done])
+    assert r.stats["graph_replays"] == 26
+    for i in range(3):
+        assert rel_err(torch.cat(got[i]), want[i]) < TOL["float32"]
 
 
 def _standout_runner(chunk, far, n):
@@ -460,7 +487,7 @@ def test_greedy_generation_through_llm_generate():
 
     hf = MovolornConfig.from_json(config_a())
     cfg = LLMConfig(model="synthetic", hf_config=hf, dtype="float32", max_num_seqs=3, kvcache_page_size=16,
-                    max_model_len=160, enforce_eager=True)
+                    max_model_len=160)
     llm = LLM(cfg, num_pages=14, device_allocator=False, max_batched_tokens=16)
     om = oracle_model(llm.model_runner.model)
     prompts = [tokens(n, 97, 30 + i) for i, n in enumerate((40, 3, 25, 1, 18))]
