@@ -214,9 +214,12 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
     pos, bm = i32([L - 1] * B), i32(slots)
 
     def decode(chunk):
+        attn.chunk = chunk
+        splits = attn.decode_splits(B, L)
+        ws = N.workspace(dev, 4 * B * H * splits * (2 + D), "bias_attn_decode")
         N.check(lib.cvllm_bias_attn_decode(N.ptr(qd), N.ptr(attn.k_cache), N.ptr(attn.v_cache), *table, N.ptr(pos),
                                            N.ptr(bm), N.ptr(attn.slopes), chunk, 1, attn.scale, N.ptr(od), B, H, G, D, D,
-                                           0, code, N.stream(dev)), "decode")
+                                           0, splits, N.ptr(ws), ws.numel(), code, N.stream(dev)), "decode")
 
     add("bias_attn_decode (no chunk, 8 x 4096)", timed(lambda: decode(0)), nbytes=2 * 2 * B * G * L * D,
         like="decode_attn_kernel")

@@ -312,8 +312,9 @@ class ModelRunner:
             def forward():
                 pk = st["packed"]
                 ids, pos, slots = pk[:bs].long(), pk[bs:2 * bs], pk[2 * bs:]
+                # max_seqlen_k: the replay serves any context length, so the key splits are sized for the longest
                 set_context(is_prefill=False, batch_mapping=slots, positions_i32=pos, token_slot=slots,
-                            max_seqlen_q=1)
+                            max_seqlen_q=1, max_seqlen_k=self.config.max_model_len)
                 hidden = self.model(ids, pos.long())
                 out = self.model.lm_head(hidden)
                 reset_context()

@@ -147,6 +147,13 @@ class BiasedChunkAttention(nn.Module):
     def qkv_width(self) -> int:
         return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
 
+    def decode_splits(self, batch: int, max_keys: int) -> int:
+        """Parts a sequence's keys are cut into for a decode step: enough CTAs for two per SM, at least 128 keys
+        per part.  `max_keys` bounds the keys a query can see (the chunk bounds it further)."""
+        keys = min(max_keys, self.chunk) if self.chunk else max_keys
+        ctas = batch * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 4)
+        return int(max(1, min(-(-296 // max(ctas, 1)), keys // 128, 64)))
+
     def forward(self, qkv: torch.Tensor) -> torch.Tensor:
         from compactor_vllm import _native as N
 
@@ -173,8 +180,11 @@ class BiasedChunkAttention(nn.Module):
                 "cvllm_bias_attn_varlen")
         else:
             assert ctx.batch_mapping.numel() == T
+            splits = self.decode_splits(T, int(ctx.max_seqlen_k))
+            ws = N.workspace(dev, 4 * T * H * splits * (2 + Dv), "bias_attn_decode") if splits > 1 else None
             N.check(lib.cvllm_bias_attn_decode(
                 N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache), *table, N.ptr(ctx.positions_i32),
                 N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), self.scale, N.ptr(out),
-                T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)), "cvllm_bias_attn_decode")
+                T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, code,
+                N.stream(dev)), "cvllm_bias_attn_decode")
         return out.view(T, H * Dv)

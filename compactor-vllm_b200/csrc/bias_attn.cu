@@ -9,6 +9,7 @@
 // The new tokens' keys are in the cache before the attention launches read it, so both read keys from one place.
 // All arithmetic is fp32; 16-bit storage only rounds q, k, v and the output.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace cvllm {
 namespace {
@@ -224,6 +225,180 @@ __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Portions, tensor-core path: bfloat16, D a multiple of 16, Dv a multiple of 8, both at most DMAX (64 or 128).
+// CTA = (64-query tile, query head), 4 warps; warp w owns query rows 16 w .. 16 w + 15 of the tile and keeps their
+// Q fragments, running maxima and sums, and output accumulators in registers.  Keys and values come in tiles of 64
+// rows through shared memory (16-byte copies out of the paged cache).  S = Q K^T and O += P V are
+// mma.sync m16n8k16 with fp32 accumulators; bias, masks and the softmax run in fp32 on the S fragments, P is rounded
+// to bfloat16 for the second product.
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <int DMAX>
+__global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q,
+    const int32_t* __restrict__ seq_start, const int32_t* __restrict__ batch_mapping,
+    const float* __restrict__ slopes, int chunk, float sink, float scale, __nv_bfloat16* __restrict__ out, int H, int G,
+    int D, int Dv) {
+  constexpr int BN = 64, LD = DMAX + 8, KS = DMAX / 16, NV = DMAX / 8;
+  __shared__ __align__(16) __nv_bfloat16 Ks[BN][LD];
+  __shared__ __align__(16) __nv_bfloat16 Vs[BN][LD];
+  __shared__ int64_t rix[BN];
+  const int b = blockIdx.y, h = blockIdx.z;
+  const int q0 = cu_q[b], n_new = cu_q[b + 1] - q0;
+  const int tile0 = blockIdx.x * BM;
+  if (tile0 >= n_new) return;
+  const int slot = batch_mapping[b];
+  const int g = h / (H / G);
+  const int rows = min(BM, n_new - tile0);
+  const int p_first = seq_start[b] + tile0, p_last = p_first + rows - 1;
+  const int lo = chunk > 0 ? (p_first / chunk) * chunk : 0;
+  const float slope = slopes ? slopes[h] : 0.f;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quad = lane >> 2, tq = lane & 3;
+  const int r_lo = warp * 16 + quad, r_hi = r_lo + 8;           // this lane's two query rows of the tile
+
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    const int col = ks * 16 + tq * 2;
+    const __nv_bfloat16* row_lo = q + ((int64_t)(q0 + tile0 + r_lo) * H + h) * D;
+    const __nv_bfloat16* row_hi = q + ((int64_t)(q0 + tile0 + r_hi) * H + h) * D;
+    const bool in = ks * 16 < D;
+    qa[ks][0] = (in && r_lo < rows) ? *reinterpret_cast<const uint32_t*>(row_lo + col) : 0u;
+    qa[ks][1] = (in && r_hi < rows) ? *reinterpret_cast<const uint32_t*>(row_hi + col) : 0u;
+    qa[ks][2] = (in && r_lo < rows) ? *reinterpret_cast<const uint32_t*>(row_lo + col + 8) : 0u;
+    qa[ks][3] = (in && r_hi < rows) ? *reinterpret_cast<const uint32_t*>(row_hi + col + 8) : 0u;
+  }
+  float m[2], l[2], o[NV][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    m[i] = sink > 0.f ? 0.f : -INFINITY;   // with a sink: its score and its term
+    l[i] = sink;
+  }
+#pragma unroll
+  for (int nb = 0; nb < NV; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nb][e] = 0.f;
+  const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(c.k);
+  const __nv_bfloat16* vc = static_cast<const __nv_bfloat16*>(c.v);
+  const int pi_lo = p_first + r_lo, pi_hi = p_first + r_hi;
+  const int lo_lo = chunk > 0 ? (pi_lo / chunk) * chunk : 0, lo_hi = chunk > 0 ? (pi_hi / chunk) * chunk : 0;
+  const int kvec = D / 8, vvec = Dv / 8;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+
+  for (int k0 = lo; k0 <= p_last; k0 += BN) {
+    __syncthreads();   // the previous tile is no longer read
+    const int nk = min(BN, p_last + 1 - k0);
+    if (tid < nk) rix[tid] = cache_row(c, slot, g, k0 + tid);
+    __syncthreads();
+    for (int i = tid; i < BN * kvec; i += 128) {
+      const int r = i / kvec, cv = i - r * kvec;
+      *reinterpret_cast<uint4*>(&Ks[r][cv * 8]) =
+          r < nk ? *reinterpret_cast<const uint4*>(kc + rix[r] * D + cv * 8) : zero4;
+    }
+    for (int i = tid; i < BN * (DMAX / 8); i += 128) {   // every column of the tile: unused ones must not hold NaN
+      const int r = i / (DMAX / 8), cv = i - r * (DMAX / 8);
+      *reinterpret_cast<uint4*>(&Vs[r][cv * 8]) =
+          (r < nk && cv < vvec) ? *reinterpret_cast<const uint4*>(vc + rix[r] * Dv + cv * 8) : zero4;
+    }
+    __syncthreads();
+    float s[BN / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < BN / 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        if (ks * 16 < D) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ks[nb * 8 + quad][ks * 16 + tq * 2]);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ks[nb * 8 + quad][ks * 16 + tq * 2 + 8]);
+          mma16816<true>(s[nb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        }
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < BN / 8; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int pj = k0 + nb * 8 + tq * 2 + (e & 1);
+        const int pi = (e & 2) ? pi_hi : pi_lo;
+        const int lo_i = (e & 2) ? lo_hi : lo_lo;
+        const bool ok = ((e & 2) ? r_hi : r_lo) < rows && pj <= pi && pj >= lo_i;
+        s[nb][e] = ok ? s[nb][e] * scale - slope * (float)(pi - pj) : -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+      mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+      const float m_new = fmaxf(m[i], mx[i]);
+      corr[i] = m_new == -INFINITY ? 1.f : __expf(m[i] - m_new);
+      m[i] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nb = 0; nb < BN / 8; ++nb)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = s[nb][e] == -INFINITY ? 0.f : __expf(s[nb][e] - m[e >> 1]);
+        s[nb][e] = p;
+        sum[e >> 1] += p;
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+      sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+      l[i] = l[i] * corr[i] + sum[i];
+    }
+#pragma unroll
+    for (int nb = 0; nb < NV; ++nb) {
+      o[nb][0] *= corr[0];
+      o[nb][1] *= corr[0];
+      o[nb][2] *= corr[1];
+      o[nb][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kb = 0; kb < BN / 16; ++kb) {
+      if (kb * 16 < nk) {
+        const uint32_t a0 = pack2<true>(s[2 * kb][0], s[2 * kb][1]), a1 = pack2<true>(s[2 * kb][2], s[2 * kb][3]);
+        const uint32_t a2 = pack2<true>(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+        const uint32_t a3 = pack2<true>(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+#pragma unroll
+        for (int nb = 0; nb < NV; nb += 2) {
+          if (nb * 8 < Dv) {
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, &Vs[kb * 16 + (lane & 15)][nb * 8 + (lane >> 4) * 8]);
+            mma16816<true>(o[nb], a0, a1, a2, a3, vb[0], vb[1]);
+            mma16816<true>(o[nb + 1], a0, a1, a2, a3, vb[2], vb[3]);
+          }
+        }
+      }
+    }
+  }
+  const float inv[2] = {l[0] > 0.f ? 1.0f / l[0] : 0.f, l[1] > 0.f ? 1.0f / l[1] : 0.f};
+#pragma unroll
+  for (int nb = 0; nb < NV; ++nb) {
+    const int col = nb * 8 + tq * 2;
+    if (col < Dv) {
+      if (r_lo < rows)
+        *reinterpret_cast<uint32_t*>(out + ((int64_t)(q0 + tile0 + r_lo) * H + h) * Dv + col) =
+            pack2<true>(o[nb][0] * inv[0], o[nb][1] * inv[0]);
+      if (r_hi < rows)
+        *reinterpret_cast<uint32_t*>(out + ((int64_t)(q0 + tile0 + r_hi) * H + h) * Dv + col) =
+            pack2<true>(o[nb][2] * inv[1], o[nb][3] * inv[1]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Decode.  CTA = (sequence, query head), 4 warps; a warp takes 32 keys at a time, one key per lane for the
 // score, one output column per lane (and every 32nd after it) for the value sum; the warps' partial softmax
 // states are merged through shared memory.
@@ -313,6 +488,234 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode, vector path (D and Dv multiples of 8, at most 256).  CTA = (key split, kv head x tile of up to four of
+// its query heads, sequence); 128 threads = 16 groups of 8 lanes.  A group takes every 16th key of the split: its
+// lanes read the key row and the value row in 16-byte pieces (lane `sub` owns elements 8 (sub + 8 i) ... + 7), the
+// dot products of the tile's heads are finished by three shuffles inside the group, and each group carries its own
+// running softmax state.  The states are merged by shuffles inside a warp, through shared memory across warps, and
+// - with more than one split - by bias_attn_decode_merge_kernel from a workspace of (max, sum, values) records.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kDecTile = 4;   // query heads per CTA
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* v);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* v) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+template <typename T, int CH>
+__global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
+    const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
+    const int32_t* __restrict__ batch_mapping, const float* __restrict__ slopes, int chunk, float sink, float scale,
+    T* __restrict__ out, float* __restrict__ part, int H, int G, int D, int Dv, int splits, int reserved_slot) {
+  __shared__ float qs[kDecTile][64 * CH];
+  __shared__ float st[4][kDecTile][2 + 64 * CH];
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int R = H / G, tiles = (R + kDecTile - 1) / kDecTile;
+  const int g = blockIdx.y / tiles, h0 = g * R + (blockIdx.y % tiles) * kDecTile;
+  const int nr = min(kDecTile, g * R + R - h0);
+  const int tid = threadIdx.x, sub = tid & 7, gid = tid >> 3, warp = tid >> 5;
+  const int slot = batch_mapping[b];
+  const int rec = 2 + Dv;
+  if (slot == reserved_slot) {
+    for (int i = tid; i < nr * Dv; i += 128) {
+      const int r = i / Dv, d = i - r * Dv;
+      if (splits == 1) out[((int64_t)b * H + h0 + r) * Dv + d] = from_f<T>(0.f);
+    }
+    if (splits > 1 && tid < nr) {
+      float* p = part + (((int64_t)b * H + h0 + tid) * splits + split) * rec;
+      p[0] = -INFINITY;
+      p[1] = 0.f;
+    }
+    return;
+  }
+  const int pi = positions[b];
+  const int lo = chunk > 0 ? (pi / chunk) * chunk : 0;
+  const int n = pi - lo + 1, per = (n + splits - 1) / splits;
+  const int k_begin = lo + split * per, k_end = min(pi + 1, k_begin + per);
+  for (int i = tid; i < kDecTile * D; i += 128) {
+    const int r = i / D, d = i - r * D;
+    qs[r][d] = r < nr ? to_f<T>(q[((int64_t)b * H + h0 + r) * D + d]) * scale : 0.f;
+  }
+  float slope[kDecTile];
+#pragma unroll
+  for (int r = 0; r < kDecTile; ++r) slope[r] = (slopes && r < nr) ? slopes[h0 + r] : 0.f;
+  __syncthreads();
+  const T* kc = static_cast<const T*>(c.k);
+  const T* vc = static_cast<const T*>(c.v);
+  float m[kDecTile], l[kDecTile], acc[kDecTile][CH * 8];
+#pragma unroll
+  for (int r = 0; r < kDecTile; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < CH * 8; ++e) acc[r][e] = 0.f;
+  }
+  const unsigned gmask = 0xffu << (tid & 24);   // the group's own lanes: groups of a warp leave the loop apart
+  for (int j = k_begin + gid; j < k_end; j += 16) {
+    const int64_t row = cache_row(c, slot, g, j);
+    float s[kDecTile];
+#pragma unroll
+    for (int r = 0; r < kDecTile; ++r) s[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int cb = (sub + 8 * i) * 8;
+      if (cb < D) {
+        float kv[8];
+        load8<T>(kc + row * D + cb, kv);
+#pragma unroll
+        for (int r = 0; r < kDecTile; ++r)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[r] = fmaf(qs[r][cb + e], kv[e], s[r]);
+      }
+    }
+    const float dist = (float)(pi - j);
+    float p[kDecTile];
+#pragma unroll
+    for (int r = 0; r < kDecTile; ++r) {
+      float v = s[r];
+      v += __shfl_xor_sync(gmask, v, 4);
+      v += __shfl_xor_sync(gmask, v, 2);
+      v += __shfl_xor_sync(gmask, v, 1);
+      v -= slope[r] * dist;
+      if (v > m[r]) {   // the same for the 8 lanes of the group
+        const float corr = expf(m[r] - v);
+        l[r] *= corr;
+#pragma unroll
+        for (int e = 0; e < CH * 8; ++e) acc[r][e] *= corr;
+        m[r] = v;
+      }
+      p[r] = expf(v - m[r]);
+      l[r] += p[r];
+    }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int cb = (sub + 8 * i) * 8;
+      if (cb < Dv) {
+        float vv[8];
+        load8<T>(vc + row * Dv + cb, vv);
+#pragma unroll
+        for (int r = 0; r < kDecTile; ++r)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[r][i * 8 + e] = fmaf(p[r], vv[e], acc[r][i * 8 + e]);
+      }
+    }
+  }
+  // the four groups of a warp (lanes differing in bits 3 and 4)
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+#pragma unroll
+    for (int r = 0; r < kDecTile; ++r) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[r], o);
+      const float lo_ = __shfl_xor_sync(0xffffffffu, l[r], o);
+      const float mn = fmaxf(m[r], mo);
+      const float fa = m[r] == -INFINITY ? 0.f : expf(m[r] - mn);
+      const float fb = mo == -INFINITY ? 0.f : expf(mo - mn);
+      l[r] = l[r] * fa + lo_ * fb;
+#pragma unroll
+      for (int e = 0; e < CH * 8; ++e) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[r][e], o);
+        acc[r][e] = acc[r][e] * fa + ao * fb;
+      }
+      m[r] = mn;
+    }
+  }
+  if ((tid & 31) < 8) {
+#pragma unroll
+    for (int r = 0; r < kDecTile; ++r) {
+      if (sub == 0) { st[warp][r][0] = m[r]; st[warp][r][1] = l[r]; }
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int cb = (sub + 8 * i) * 8;
+        if (cb < Dv)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) st[warp][r][2 + cb + e] = acc[r][i * 8 + e];
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < nr * Dv; i += 128) {
+    const int r = i / Dv, d = i - r * Dv;
+    float mm = (splits == 1 && sink > 0.f) ? 0.f : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, st[w][r][0]);
+    float ll = (splits == 1 && sink > 0.f) ? sink * expf(0.f - mm) : 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = st[w][r][0];
+      if (mw == -INFINITY) continue;
+      const float f = expf(mw - mm);
+      ll += st[w][r][1] * f;
+      a += st[w][r][2 + d] * f;
+    }
+    if (splits == 1) {
+      out[((int64_t)b * H + h0 + r) * Dv + d] = from_f<T>(ll > 0.f ? a / ll : 0.f);
+    } else {
+      float* pr = part + (((int64_t)b * H + h0 + r) * splits + split) * rec;
+      if (d == 0) { pr[0] = mm; pr[1] = ll; }
+      pr[2 + d] = a;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) bias_attn_decode_merge_kernel(const float* __restrict__ part, float sink,
+                                                                     T* __restrict__ out, int Dv, int splits) {
+  const int64_t bh = blockIdx.x;
+  const int rec = 2 + Dv;
+  const float* p = part + bh * splits * rec;
+  float mm = sink > 0.f ? 0.f : -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[s * rec]);
+  float ll = sink > 0.f ? sink * expf(0.f - mm) : 0.f;
+  for (int s = 0; s < splits; ++s)
+    if (p[s * rec] != -INFINITY) ll += p[s * rec + 1] * expf(p[s * rec] - mm);
+  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+  for (int d = threadIdx.x; d < Dv; d += 128) {
+    float a = 0.f;
+    for (int s = 0; s < splits; ++s)
+      if (p[s * rec] != -INFINITY) a += p[s * rec + 2 + d] * expf(p[s * rec] - mm);
+    out[bh * Dv + d] = from_f<T>(a * inv);
+  }
+}
+
+template <typename T>
+int launch_decode_split(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
+                        const float* slopes, int chunk, float sink, float scale, void* out, float* part, int B, int H,
+                        int G, int D, int Dv, int splits, int reserved_slot, cudaStream_t st) {
+  const int R = H / G, tiles = cdiv(R, kDecTile);
+  dim3 grid(splits, G * tiles, B);
+  const int ch = cdiv(D > Dv ? D : Dv, 64);
+#define CVLLM_GO(CH)                                                                                             \
+  bias_attn_decode_split_kernel<T, CH><<<grid, 128, 0, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, \
+                                                             chunk, sink, scale, static_cast<T*>(out), part, H, G, D, \
+                                                             Dv, splits, reserved_slot)
+  if (ch == 1) CVLLM_GO(1);
+  else if (ch == 2) CVLLM_GO(2);
+  else if (ch == 3) CVLLM_GO(3);
+  else CVLLM_GO(4);
+#undef CVLLM_GO
+  CVLLM_CHECK_LAUNCH();
+  if (splits > 1) {
+    bias_attn_decode_merge_kernel<T><<<B * H, 128, 0, st>>>(part, sink, static_cast<T*>(out), Dv, splits);
+    CVLLM_CHECK_LAUNCH();
+  }
+  return CVLLM_OK;
+}
+
 size_t varlen_smem(int BN, int D, int Dv) {
   return sizeof(float) * ((size_t)BM * (D + 1) + (size_t)BN * (D + 1) + (size_t)BN * Dv + (size_t)BM * (BN + 1));
 }
@@ -398,6 +801,19 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
 #define CVLLM_GO(T, BN) \
   return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B, \
                              max_new, H, G, D, Dv, st)
+  if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && !test_options().bias_attn_fma.load()) {
+    dim3 grid(cdiv(max_new, BM), B, H);
+    if (D <= 64 && Dv <= 64)
+      bias_attn_varlen_mma_kernel<64><<<grid, 128, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(q), c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale,
+          static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
+    else
+      bias_attn_varlen_mma_kernel<128><<<grid, 128, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(q), c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale,
+          static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
+    CVLLM_CHECK_LAUNCH();
+    return CVLLM_OK;
+  }
   if (dtype == CVLLM_BF16) {
     if (bn == 64) CVLLM_GO(__nv_bfloat16, 64);
     CVLLM_GO(__nv_bfloat16, 32);
@@ -411,14 +827,30 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
                                       const int32_t* page_table, int64_t table_stride_slot, int64_t table_stride_head,
                                       int page_size, const int32_t* positions, const int32_t* batch_mapping,
                                       const float* slopes, int chunk, int sink, float scale, void* out, int B, int H,
-                                      int G, int D, int Dv, int reserved_slot, int dtype, cvllm_stream_t stream) {
-  CVLLM_CHECK_ARG(B >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
+                                      int G, int D, int Dv, int reserved_slot, int splits, float* workspace,
+                                      size_t workspace_bytes, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0 && splits >= 1);
   if (B == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && positions && batch_mapping && out && check_dtype(dtype) &&
                   page_size > 0);
-  CVLLM_CHECK_SUPPORTED(Dv <= 32 * kDecCols && H <= 65535);
+  CVLLM_CHECK_SUPPORTED(Dv <= 32 * kDecCols && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
   PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  if (D % 8 == 0 && Dv % 8 == 0 && D <= 256 && Dv <= 256) {
+    if (splits > 1) {
+      CVLLM_CHECK_ARG(workspace != nullptr);
+      if (workspace_bytes < sizeof(float) * (size_t)B * H * splits * (2 + Dv)) {
+        set_last_error("decode workspace too small");
+        return CVLLM_E_WORKSPACE;
+      }
+    }
+    const float fs = sink ? 1.f : 0.f;
+    if (dtype == CVLLM_BF16)
+      return launch_decode_split<__nv_bfloat16>(q, c, positions, batch_mapping, slopes, chunk, fs, scale, out,
+                                                workspace, B, H, G, D, Dv, splits, reserved_slot, st);
+    return launch_decode_split<float>(q, c, positions, batch_mapping, slopes, chunk, fs, scale, out, workspace, B, H,
+                                      G, D, Dv, splits, reserved_slot, st);
+  }
   const size_t smem = sizeof(float) * ((size_t)D + (size_t)kDecWarps * (2 + Dv));
   CVLLM_CHECK_SUPPORTED(smem <= 48 * 1024);
   dim3 grid(B, H);

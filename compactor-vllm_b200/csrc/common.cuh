@@ -91,6 +91,7 @@ struct TestOptions {
   std::atomic<int> grs_probe{0};              // gemm_reduce timing probes (bit mask; results are wrong)
   std::atomic<uint64_t> grs_debug_host_ptr{0};  // pinned host buffer for gemm_reduce's timeout records
   std::atomic<int> grs_rows_per_round{0};     // > 0: rows per reduce round of gemm_reduce (multiple of 256)
+  std::atomic<int> bias_attn_fma{0};          // 1: 16-bit portions of the biased attention on the fp32 FMA kernel
 };
 TestOptions& test_options();
 

@@ -66,6 +66,7 @@ uint64_t cvllm_launch_count(void);
  *   "grs_rows_per_round" r   rows per reduce round of cvllm_gemm_allreduce (multiple of 256; 0 = default 256)
  *   "grs_probe" mask         timing probes of cvllm_gemm_allreduce (results are wrong on purpose: 1 no TMA loads,
  *                            2 no UMMA, 4 no stores, 8 no reduce, 16 no L2 hints)
+ *   "bias_attn_fma" 1|0      bfloat16 portions of cvllm_bias_attn_varlen on the fp32 FMA kernel instead of mma.sync (A/B)
  *   "grs_debug_host_ptr" p   pinned host buffer (64 words per CTA) for cvllm_gemm_allreduce's timeout records
  * Returns CVLLM_E_ARG for an unknown name. */
 int cvllm_set_test_option(const char* name, double value);
@@ -463,12 +464,14 @@ int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cac
                            int H, int G, int D, int Dv, int dtype, cvllm_stream_t stream);
 
 /* Decode: one query per sequence at position positions[b] (its key is in the cache already).  q [B, H, D],
- * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 256. */
+ * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 256.  With D and Dv multiples of 8 (and D <= 256) the keys
+ * of a sequence are cut into `splits` parts that run on CTAs of their own; splits > 1 needs a workspace of
+ * 4 * B * H * splits * (2 + Dv) bytes.  Other sizes run one CTA per (sequence, head) and ignore `splits`. */
 int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
                            int64_t table_stride_slot, int64_t table_stride_head, int page_size,
                            const int32_t* positions, const int32_t* batch_mapping, const float* slopes, int chunk,
                            int sink, float scale, void* out, int B, int H, int G, int D, int Dv, int reserved_slot,
-                           int dtype, cvllm_stream_t stream);
+                           int splits, float* workspace, size_t workspace_bytes, int dtype, cvllm_stream_t stream);
 
 #ifdef __cplusplus
 }

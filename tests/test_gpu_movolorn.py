@@ -296,6 +296,22 @@ def test_long_decoding_over_pages_and_chunks(eager):
     assert (r.stats["graph_replays"] > 0) == (not eager)
 
 
+@pytest.mark.parametrize("dtype,eager", [("float32", True), ("float32", False), ("bfloat16", True)])
+def test_decoding_far_into_an_unchunked_sequence(dtype, eager):
+    """No chunking: hundreds of keys per query, which the decode kernel cuts into several parts that are merged."""
+    from oracle import movolorn as O
+
+    r = make_runner(config_b(chunk=0, heads=4, kv_heads=2), dtype, pages=40, page_size=16, eager=eager)
+    assert r.model.layers[0].mixer.attn.decode_splits(1, 600) > 1
+    om = oracle_model(r.model)
+    toks = tokens(540, 64, 8)
+    want = O.forward(om, toks)
+    seq = new_seq()
+    out = [feed(r, seq, toks[:520])] + [feed(r, seq, [t]) for t in toks[520:]]
+    r.release([seq])
+    assert close(torch.cat(out), want, dtype)
+
+
 def test_graph_decode_batches_with_padding_rows():
     """Three decoding requests (padded to four rows in the graph) of unequal lengths, one of which ends early."""
     from oracle import movolorn as O
@@ -472,6 +488,50 @@ def test_other_attention_sizes(over):
     assert rel_err(run_in_portions(r, toks, [70]), want) < TOL["float32"]
     assert rel_err(run_in_portions(r, toks, [37, 2, 1]), want) < TOL["float32"]
     assert rel_err(run_in_portions(r, toks[:40], [1]), want[:40]) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dim,vdim,chunk", [(32, 40, 50), (64, 64, 0), (80, 128, 33), (128, 24, 70), (16, 8, 5)])
+def test_bfloat16_portions_on_tensor_cores(dim, vdim, chunk):
+    """Head sizes the mma.sync portion kernel takes (key size a multiple of 16, value size of 8): against the oracle,
+    and against the fp32 FMA kernel on the same bfloat16 inputs (they differ only by the rounding of P)."""
+    from compactor_vllm import _native as N
+    from oracle import movolorn as O
+
+    cfg = {"architecture": "Movolorn", "vocab": 80, "width": 48, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+           "layers": [{"type": "attention", "mixer": attn_cfg(6, 2, dim, vdim, chunk), "mlp": {"kind": "dense", "ff": 64}},
+                      {"type": "attention", "mixer": attn_cfg(2, 2, dim, vdim, chunk), "mlp": None}]}
+    r = make_runner(cfg, "bfloat16", pages=24, page_size=16)
+    om = oracle_model(r.model)
+    reqs = [tokens(150, 80, 50), tokens(67, 80, 51)]
+    want = [O.forward(om, t) for t in reqs]
+
+    def run():
+        seqs, got, at = [new_seq(), new_seq()], [[], []], [0, 0]
+        for step in ([(0, 70), (1, 3)], [(0, 64), (1, 64)], [(0, 16)]):
+            entries, spans, base = [], [], 0
+            for i, n in step:
+                part = reqs[i][at[i]:at[i] + n]
+                seqs[i].prompt_token_ids.extend(part)
+                entries.append((seqs[i], part))
+                spans.append((i, base, len(part)))
+                at[i] += len(part)
+                base += len(part)
+            logits = r.run_step(entries, rows=list(range(base)))
+            for i, b_, n in spans:
+                got[i].append(logits[b_:b_ + n])
+        r.release(seqs)
+        return [torch.cat(g_).float().cpu() for g_ in got]
+
+    mma = run()
+    N.set_test_option("bias_attn_fma", 1)
+    try:
+        fma = run()
+    finally:
+        N.set_test_option("bias_attn_fma", 0)
+    for i in range(2):
+        assert close(mma[i], want[i], "bfloat16") and close(fma[i], want[i], "bfloat16")
+        assert rel_err(mma[i], fma[i]) < 0.05
+        assert row_errs(mma[i], fma[i]).median() < 0.01
 
 
 # ------------------------------------------------------------------------------ generation through the entry point
