@@ -15,13 +15,14 @@ from compactor_vllm.utils.context import get_context
 ACT_SILU, ACT_GELU_TANH = 0, 1
 
 
-def gated_act(x: torch.Tensor, kind: int) -> torch.Tensor:
-    """x [T, 2F] = [gate | up] -> act(gate) * up, [T, F]; kind ACT_SILU or ACT_GELU_TANH (fp32 inside)."""
+def gated_act(x: torch.Tensor, kind: int, rows: int | None = None) -> torch.Tensor:
+    """x [T, 2F] = [gate | up] -> act(gate) * up, [T, F]; kind ACT_SILU or ACT_GELU_TANH (fp32 inside).
+    `rows`: only the first so many rows are computed (the output still has T rows)."""
     T, F2 = x.shape
     assert F2 % 2 == 0 and x.stride(1) == 1
     out = torch.empty((T, F2 // 2), dtype=x.dtype, device=x.device)
-    rc = N.lib().cvllm_gated_act(N.ptr(x), x.stride(0), N.ptr(out), out.stride(0), T, F2 // 2, int(kind),
-                                 N.block_dtype_code(x.dtype), N.stream(x.device))
+    rc = N.lib().cvllm_gated_act(N.ptr(x), x.stride(0), N.ptr(out), out.stride(0), T if rows is None else int(rows),
+                                 F2 // 2, int(kind), N.block_dtype_code(x.dtype), N.stream(x.device))
     N.check(rc, "cvllm_gated_act")
     return out
 
@@ -58,14 +59,17 @@ class RoutedExperts(nn.Module):
     """Mixture of `experts` gated experts and `identity` experts that return their input, `top` per token, with
     group-limited choice, a correction that shifts the choice but not the weights, and an optional shared expert.
 
-    The router runs in fp32.  Portions: tokens are sorted by expert, each expert with tokens runs its two GEMMs on
-    its segment (the per-expert counts cross to the host once per layer).  Few tokens (decode steps, and any step of
+    The router runs in fp32.  Portions: (token, choice) pairs are sorted by expert; in bfloat16 (sizes multiples of 8)
+    the two projections are library grouped GEMMs over the segments (`torch._grouped_mm`, segment ends on the device);
+    otherwise - float32, odd sizes - each expert with tokens runs its two GEMMs on its segment and the per-expert
+    counts cross to the host once per layer.  Few tokens (decode steps, and any step of
     at most `SMALL_STEP` tokens): `cvllm_expert_gemv` reads each chosen expert's rows straight from the routing
     indices on the device, so the step has no host round trip and can be captured in a CUDA graph.  Either way the
     combine kernel sums the `top` outputs of every token (identity experts and the shared expert included) in fp32.
     Returns fp32 [T, width]."""
 
     SMALL_STEP = 8
+    grouped_gemm = hasattr(torch, "_grouped_mm")     # False: the per-expert loop also in bfloat16 (tests compare them)
 
     def __init__(self, width: int, ff: int, experts: int, identity: int, top: int, groups: int, keep: int,
                  shared_ff: int, act: int = ACT_SILU, dtype: torch.dtype | None = None):
@@ -97,20 +101,35 @@ class RoutedExperts(nn.Module):
             N.check(lib.cvllm_moe_combine(N.ptr(ys), None, N.ptr(wts), self.top, N.ptr(idx), self.n_real, N.ptr(x),
                                           N.ptr(shared), N.ptr(out), T, W, code, st), "cvllm_moe_combine")
             return out
+        # pairs sorted by expert (identity experts' pairs come last and are never multiplied); every buffer has
+        # T * top rows whatever the routing, so the allocator sees the same sizes every step
         flat = idx.view(-1).long()
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=self.n_real + self.n_identity)[: self.n_real].tolist()
-        n_rows = sum(counts)
         pos = torch.empty_like(order, dtype=torch.int32)
         pos[order] = torch.arange(order.numel(), dtype=torch.int32, device=x.device)
-        ys = torch.empty((max(n_rows, 1), W), dtype=x.dtype, device=x.device)
-        if n_rows:
-            xs = x.index_select(0, order[:n_rows] // self.top)
+        xs = x.index_select(0, order // self.top)
+        counts = torch.zeros(self.n_real + self.n_identity, dtype=torch.int32, device=x.device)
+        counts.index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
+        if self.grouped_gemm and x.dtype == torch.bfloat16 and W % 8 == 0 and self.ff % 8 == 0:
+            # library grouped GEMM: segment ends stay on the device, one launch per projection, no host round trip
+            # and no per-shape algorithm search (a plain GEMM with a row count it has not seen costs milliseconds)
+            ends = counts[: self.n_real].cumsum(0).to(torch.int32)
+            gu = torch._grouped_mm(xs, self.gate_up.transpose(1, 2), offs=ends)
+            ys = torch._grouped_mm(gated_act(gu, self.act), self.down.transpose(1, 2), offs=ends)
+        else:
+            host_counts = counts[: self.n_real].tolist()
+            gu = torch.empty((order.numel(), 2 * self.ff), dtype=x.dtype, device=x.device)
+            ys = torch.empty((order.numel(), W), dtype=x.dtype, device=x.device)
             off = 0
-            for e, c in enumerate(counts):
+            for e, c in enumerate(host_counts):
                 if c:
-                    a = gated_act(F.linear(xs[off:off + c], self.gate_up[e]), self.act)
-                    torch.mm(a, self.down[e].t(), out=ys[off:off + c])
+                    torch.mm(xs[off:off + c], self.gate_up[e].t(), out=gu[off:off + c])
+                    off += c
+            a = gated_act(gu, self.act, rows=off)
+            off = 0
+            for e, c in enumerate(host_counts):
+                if c:
+                    torch.mm(a[off:off + c], self.down[e].t(), out=ys[off:off + c])
                     off += c
         N.check(lib.cvllm_moe_combine(N.ptr(ys), N.ptr(pos), N.ptr(wts), self.top, N.ptr(idx), self.n_real, N.ptr(x),
                                       N.ptr(shared), N.ptr(out), T, W, code, st), "cvllm_moe_combine")

@@ -98,6 +98,49 @@ __global__ void gated_act_kernel(const T* __restrict__ x, int64_t x_stride, T* _
   }
 }
 
+// the same, eight elements per thread with 16-byte loads (F and both strides multiples of 8, 16-byte aligned bases)
+template <typename T, int KIND>
+__global__ void gated_act_vec_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ out,
+                                     int64_t o_stride, int64_t rows, int F) {
+  const int F8 = F / 8;
+  const int64_t total = rows * (int64_t)F8;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / F8;
+    const int f = (int)(i - t * F8) * 8;
+    float g[8], u[8];
+    const T* gp = x + t * x_stride + f;
+    T* op = out + t * o_stride + f;
+    if constexpr (sizeof(T) == 2) {
+      const uint4 a = ldg_nc_v4(gp), b = ldg_nc_v4(gp + F);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        g[2 * k] = __uint_as_float(aw[k] << 16);
+        g[2 * k + 1] = __uint_as_float(aw[k] & 0xffff0000u);
+        u[2 * k] = __uint_as_float(bw[k] << 16);
+        u[2 * k + 1] = __uint_as_float(bw[k] & 0xffff0000u);
+      }
+      uint32_t r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float lo = (KIND == 0 ? act_silu(g[2 * k]) : act_gelu_tanh(g[2 * k])) * u[2 * k];
+        const float hi = (KIND == 0 ? act_silu(g[2 * k + 1]) : act_gelu_tanh(g[2 * k + 1])) * u[2 * k + 1];
+        r[k] = pack2<true>(lo, hi);
+      }
+      *reinterpret_cast<uint4*>(op) = make_uint4(r[0], r[1], r[2], r[3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        g[k] = to_f<T>(gp[k]);
+        u[k] = to_f<T>(gp[F + k]);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) op[k] = from_f<T>((KIND == 0 ? act_silu(g[k]) : act_gelu_tanh(g[k])) * u[k]);
+    }
+  }
+}
+
 // Lowest index among the largest values of v[0..n) (lanes strided), then the same answer in every lane.
 __device__ __forceinline__ int warp_argmax(const float* v, int n, float* best_out) {
   const int lane = threadIdx.x & 31;
@@ -281,13 +324,18 @@ extern "C" int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64
   auto st = static_cast<cudaStream_t>(stream);
   const int64_t total = rows * (int64_t)F;
   const int grid = (int)((total + 255) / 256 < (int64_t)sm_count() * 16 ? (total + 255) / 256 : (int64_t)sm_count() * 16);
+  const bool vec = F % 8 == 0 && x_stride % 8 == 0 && o_stride % 8 == 0 && aligned16(x) && aligned16(out);
 #define CVLLM_GATED(T, K)                                                                                      \
-  gated_act_kernel<T, K><<<grid, 256, 0, st>>>(static_cast<const T*>(x), x_stride, static_cast<T*>(out),       \
-                                               o_stride, rows, F)
+  if (vec)                                                                                                     \
+    gated_act_vec_kernel<T, K><<<(grid + 7) / 8, 256, 0, st>>>(static_cast<const T*>(x), x_stride,             \
+                                                               static_cast<T*>(out), o_stride, rows, F);       \
+  else                                                                                                         \
+    gated_act_kernel<T, K><<<grid, 256, 0, st>>>(static_cast<const T*>(x), x_stride, static_cast<T*>(out),     \
+                                                 o_stride, rows, F)
   if (dtype == CVLLM_BF16) {
-    if (kind == 0) CVLLM_GATED(__nv_bfloat16, 0); else CVLLM_GATED(__nv_bfloat16, 1);
+    if (kind == 0) { CVLLM_GATED(__nv_bfloat16, 0); } else { CVLLM_GATED(__nv_bfloat16, 1); }
   } else {
-    if (kind == 0) CVLLM_GATED(float, 0); else CVLLM_GATED(float, 1);
+    if (kind == 0) { CVLLM_GATED(float, 0); } else { CVLLM_GATED(float, 1); }
   }
 #undef CVLLM_GATED
   CVLLM_CHECK_LAUNCH();

@@ -490,6 +490,46 @@ def test_other_attention_sizes(over):
     assert rel_err(run_in_portions(r, toks[:40], [1]), want[:40]) < TOL["float32"]
 
 
+def test_routed_experts_grouped_and_looped_products_agree():
+    """bfloat16 with sizes that are multiples of 8 takes the grouped-GEMM path; the per-expert loop and the small-step
+    kernel must give the same layer output, and all of them the oracle's."""
+    from compactor_vllm.layers.moe import ACT_SILU, RoutedExperts
+    from compactor_vllm.utils.context import reset_context, set_context
+    from oracle import movolorn as O
+
+    W, ff, E, ident = 48, 24, 6, 2
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(DEV):
+            m = RoutedExperts(W, ff, E, ident, 3, 4, 2, 32, ACT_SILU, torch.bfloat16)
+    finally:
+        torch.set_default_dtype(prev)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            p.copy_((torch.randn(p.shape, generator=g, device=DEV) * (0.1 if name == "correction" else p.shape[-1] ** -0.5)))
+        x = torch.randn(200, W, generator=g, device=DEV).to(torch.bfloat16)
+        f = lambda t: t.detach().float().cpu()
+        gu, dn, sg = f(m.gate_up), f(m.down), f(m.shared.gate_up_proj.weight)
+        om = {"kind": "moe", "router": f(m.router), "correction": f(m.correction), "top": 3, "groups": 4, "keep": 2,
+              "identity": ident, "experts": [{"gate": gu[e, :ff], "up": gu[e, ff:], "down": dn[e]} for e in range(E)],
+              "shared": {"gate": sg[:32], "up": sg[32:], "down": f(m.shared.down_proj.weight)}}
+        want = O.moe_ff(x.float().cpu(), om)
+        set_context(is_prefill=True)
+        assert m.grouped_gemm
+        grouped = m(x).cpu()
+        m.grouped_gemm = False
+        looped = m(x).cpu()
+        set_context(is_prefill=False)
+        small = m(x).cpu()
+        reset_context()
+    for got in (grouped, looped, small):
+        e = row_errs(got, want)
+        assert e.median() < 0.02 and e.max() < 0.2      # a flipped close call of the router may move single rows
+    assert row_errs(grouped, looped).median() < 5e-3 and row_errs(small, looped).median() < 5e-3
+
+
 @pytest.mark.parametrize("dim,vdim,chunk", [(32, 40, 50), (64, 64, 0), (80, 128, 33), (128, 24, 70), (16, 8, 5)])
 def test_bfloat16_portions_on_tensor_cores(dim, vdim, chunk):
     """Head sizes the mma.sync portion kernel takes (key size a multiple of 16, value size of 8): against the oracle,
