@@ -148,11 +148,12 @@ class BiasedChunkAttention(nn.Module):
         return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
 
     def decode_splits(self, batch: int, max_keys: int) -> int:
-        """Parts a sequence's keys are cut into for a decode step: enough CTAs for two per SM, at least 128 keys
-        per part.  `max_keys` bounds the keys a query can see (the chunk bounds it further)."""
+        """Parts a sequence's keys are cut into for a decode step: as many as keep all CTAs in ONE wave of two per SM
+        (148 SMs), at least 128 keys per part.  `max_keys` bounds the keys a query can see (the chunk bounds it
+        further)."""
         keys = min(max_keys, self.chunk) if self.chunk else max_keys
         ctas = batch * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 4)
-        return int(max(1, min(-(-296 // max(ctas, 1)), keys // 128, 64)))
+        return int(max(1, min(296 // max(ctas, 1), keys // 128, 64)))
 
     def forward(self, qkv: torch.Tensor) -> torch.Tensor:
         from compactor_vllm import _native as N

@@ -566,53 +566,91 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
     for (int e = 0; e < CH * 8; ++e) acc[r][e] = 0.f;
   }
   const unsigned gmask = 0xffu << (tid & 24);   // the group's own lanes: groups of a warp leave the loop apart
-  for (int j = k_begin + gid; j < k_end; j += 16) {
-    const int64_t row = cache_row(c, slot, g, j);
-    float s[kDecTile];
+  // the lane's slice of the tile's queries stays in registers when it is small enough (D <= 128)
+  constexpr bool kQInRegs = CH <= 2;
+  float qr[kQInRegs ? kDecTile : 1][kQInRegs ? CH * 8 : 1];
+  if constexpr (kQInRegs) {
 #pragma unroll
-    for (int r = 0; r < kDecTile; ++r) s[r] = 0.f;
+    for (int r = 0; r < kDecTile; ++r)
 #pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const int cb = (sub + 8 * i) * 8;
-      if (cb < D) {
-        float kv[8];
-        load8<T>(kc + row * D + cb, kv);
+      for (int i = 0; i < CH; ++i) {
+        const int cb = (sub + 8 * i) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) qr[r][i * 8 + e] = cb < D ? qs[r][cb + e] : 0.f;
+      }
+  }
+  // two keys of the group per pass (j and j + 16): the loads of both are in flight before either is used
+  for (int j = k_begin + gid; j < k_end; j += 32) {
+    const bool two = j + 16 < k_end;
+    const int64_t row[2] = {cache_row(c, slot, g, j), two ? cache_row(c, slot, g, j + 16) : 0};
+    float kv[2][CH][8];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int cb = (sub + 8 * i) * 8;
+        if (cb < D && (u == 0 || two)) load8<T>(kc + row[u] * D + cb, kv[u][i]);
+        else
+#pragma unroll
+          for (int e = 0; e < 8; ++e) kv[u][i][e] = 0.f;
+      }
+    float vv[2][CH][8];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int cb = (sub + 8 * i) * 8;
+        if (cb < Dv && (u == 0 || two)) load8<T>(vc + row[u] * Dv + cb, vv[u][i]);
+        else
+#pragma unroll
+          for (int e = 0; e < 8; ++e) vv[u][i][e] = 0.f;
+      }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !two) break;
+      float s[kDecTile];
+#pragma unroll
+      for (int r = 0; r < kDecTile; ++r) s[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int cb = (sub + 8 * i) * 8;
+        if (cb < D) {
+#pragma unroll
+          for (int r = 0; r < kDecTile; ++r)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float qv;
+              if constexpr (kQInRegs) qv = qr[r][i * 8 + e];
+              else qv = qs[r][cb + e];
+              s[r] = fmaf(qv, kv[u][i][e], s[r]);
+            }
+        }
+      }
+      const float dist = (float)(pi - (j + 16 * u));
+      float p[kDecTile];
+#pragma unroll
+      for (int r = 0; r < kDecTile; ++r) {
+        float v = s[r];
+        v += __shfl_xor_sync(gmask, v, 4);
+        v += __shfl_xor_sync(gmask, v, 2);
+        v += __shfl_xor_sync(gmask, v, 1);
+        v -= slope[r] * dist;
+        if (v > m[r]) {   // the same for the 8 lanes of the group
+          const float corr = expf(m[r] - v);
+          l[r] *= corr;
+#pragma unroll
+          for (int e = 0; e < CH * 8; ++e) acc[r][e] *= corr;
+          m[r] = v;
+        }
+        p[r] = expf(v - m[r]);
+        l[r] += p[r];
+      }
+#pragma unroll
+      for (int i = 0; i < CH; ++i)
 #pragma unroll
         for (int r = 0; r < kDecTile; ++r)
 #pragma unroll
-          for (int e = 0; e < 8; ++e) s[r] = fmaf(qs[r][cb + e], kv[e], s[r]);
-      }
-    }
-    const float dist = (float)(pi - j);
-    float p[kDecTile];
-#pragma unroll
-    for (int r = 0; r < kDecTile; ++r) {
-      float v = s[r];
-      v += __shfl_xor_sync(gmask, v, 4);
-      v += __shfl_xor_sync(gmask, v, 2);
-      v += __shfl_xor_sync(gmask, v, 1);
-      v -= slope[r] * dist;
-      if (v > m[r]) {   // the same for the 8 lanes of the group
-        const float corr = expf(m[r] - v);
-        l[r] *= corr;
-#pragma unroll
-        for (int e = 0; e < CH * 8; ++e) acc[r][e] *= corr;
-        m[r] = v;
-      }
-      p[r] = expf(v - m[r]);
-      l[r] += p[r];
-    }
-#pragma unroll
-    for (int i = 0; i < CH; ++i) {
-      const int cb = (sub + 8 * i) * 8;
-      if (cb < Dv) {
-        float vv[8];
-        load8<T>(vc + row * Dv + cb, vv);
-#pragma unroll
-        for (int r = 0; r < kDecTile; ++r)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) acc[r][i * 8 + e] = fmaf(p[r], vv[e], acc[r][i * 8 + e]);
-      }
+          for (int e = 0; e < 8; ++e) acc[r][i * 8 + e] = fmaf(p[r], vv[u][i][e], acc[r][i * 8 + e]);
     }
   }
   // the four groups of a warp (lanes differing in bits 3 and 4)
