@@ -34,11 +34,21 @@ struct PagedKV {
   const int32_t* table;     // [slots, G, P]
   int64_t table_stride_slot, table_stride_head;
   int page_size;
+  int page_shift;           // log2(page_size) when that is a power of two, else -1
 };
 
+inline PagedKV make_paged(const void* k, const void* v, const int32_t* table, int64_t stride_slot, int64_t stride_head,
+                          int page_size) {
+  int shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (shift = 0; (1 << shift) < page_size; ++shift) {}
+  return PagedKV{k, v, table, stride_slot, stride_head, page_size, shift};
+}
+
 __device__ __forceinline__ int64_t cache_row(const PagedKV& c, int slot, int g, int pos) {
-  const int page = c.table[slot * c.table_stride_slot + g * c.table_stride_head + pos / c.page_size];
-  return (int64_t)page * c.page_size + pos % c.page_size;
+  const int lp = c.page_shift >= 0 ? pos >> c.page_shift : pos / c.page_size;
+  const int page = c.table[slot * c.table_stride_slot + g * c.table_stride_head + lp];
+  return (int64_t)page * c.page_size + (pos - lp * c.page_size);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -239,6 +249,22 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
                : "r"(addr));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// 16 bytes global -> shared without passing through registers; bytes == 0 writes zeros and reads nothing
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int bytes) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(addr), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <int DMAX>
 __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     const __nv_bfloat16* __restrict__ q, PagedKV c, const int32_t* __restrict__ cu_q,
@@ -246,21 +272,44 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     const float* __restrict__ slopes, int chunk, float sink, float scale, __nv_bfloat16* __restrict__ out, int H, int G,
     int D, int Dv) {
   constexpr int BN = 64, LD = DMAX + 8, KS = DMAX / 16, NV = DMAX / 8;
-  __shared__ __align__(16) __nv_bfloat16 Ks[BN][LD];
-  __shared__ __align__(16) __nv_bfloat16 Vs[BN][LD];
-  __shared__ int64_t rix[BN];
+  constexpr float kL2e = 1.4426950408889634f;   // scores in log2 units: one ex2.approx per exponential
+  typedef __nv_bfloat16 Tile[BN][LD];
+  extern __shared__ __align__(16) unsigned char dyn_smem[];
+  Tile* Ks = reinterpret_cast<Tile*>(dyn_smem);   // two stages of keys, then two stages of values
+  Tile* Vs = Ks + 2;
   const int b = blockIdx.y, h = blockIdx.z;
   const int q0 = cu_q[b], n_new = cu_q[b + 1] - q0;
-  const int tile0 = blockIdx.x * BM;
+  // the latest (heaviest) query tiles first
+  const int tile0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * BM;
   if (tile0 >= n_new) return;
   const int slot = batch_mapping[b];
   const int g = h / (H / G);
   const int rows = min(BM, n_new - tile0);
   const int p_first = seq_start[b] + tile0, p_last = p_first + rows - 1;
   const int lo = chunk > 0 ? (p_first / chunk) * chunk : 0;
-  const float slope = slopes ? slopes[h] : 0.f;
+  const float slope2 = slopes ? slopes[h] * kL2e : 0.f;
+  const float scale2 = scale * kL2e;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, quad = lane >> 2, tq = lane & 3;
   const int r_lo = warp * 16 + quad, r_hi = r_lo + 8;           // this lane's two query rows of the tile
+  const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(c.k);
+  const __nv_bfloat16* vc = static_cast<const __nv_bfloat16*>(c.v);
+  const int kvec = D / 8, vvec = Dv / 8;
+
+  auto issue_tile = [&](int stage, int k0) {
+    const int nk = min(BN, p_last + 1 - k0);
+    for (int i = tid; i < BN * kvec; i += 128) {
+      const int r = i / kvec, cv = i - r * kvec;
+      const bool in = r < nk;
+      cp_async16(&Ks[stage][r][cv * 8], in ? kc + cache_row(c, slot, g, k0 + r) * D + cv * 8 : kc, in ? 16 : 0);
+    }
+    for (int i = tid; i < BN * (DMAX / 8); i += 128) {   // every column of the tile: unused ones must not hold NaN
+      const int r = i / (DMAX / 8), cv = i - r * (DMAX / 8);
+      const bool in = r < nk && cv < vvec;
+      cp_async16(&Vs[stage][r][cv * 8], in ? vc + cache_row(c, slot, g, k0 + r) * Dv + cv * 8 : vc, in ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+  issue_tile(0, lo);
 
   uint32_t qa[KS][4];
 #pragma unroll
@@ -284,63 +333,71 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
   for (int nb = 0; nb < NV; ++nb)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[nb][e] = 0.f;
-  const __nv_bfloat16* kc = static_cast<const __nv_bfloat16*>(c.k);
-  const __nv_bfloat16* vc = static_cast<const __nv_bfloat16*>(c.v);
   const int pi_lo = p_first + r_lo, pi_hi = p_first + r_hi;
   const int lo_lo = chunk > 0 ? (pi_lo / chunk) * chunk : 0, lo_hi = chunk > 0 ? (pi_hi / chunk) * chunk : 0;
-  const int kvec = D / 8, vvec = Dv / 8;
-  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  // a tile needs no masks for this warp when all its keys are at or before the warp's first row and inside the
+  // chunk of the warp's last row (rows beyond `rows` are never written, their values do not matter)
+  const int warp_first = p_first + warp * 16;
+  const int warp_lo = chunk > 0 ? ((warp_first + 15) / chunk) * chunk : 0;
 
-  for (int k0 = lo; k0 <= p_last; k0 += BN) {
-    __syncthreads();   // the previous tile is no longer read
+  int stage = 0;
+  for (int k0 = lo; k0 <= p_last; k0 += BN, stage ^= 1) {
     const int nk = min(BN, p_last + 1 - k0);
-    if (tid < nk) rix[tid] = cache_row(c, slot, g, k0 + tid);
-    __syncthreads();
-    for (int i = tid; i < BN * kvec; i += 128) {
-      const int r = i / kvec, cv = i - r * kvec;
-      *reinterpret_cast<uint4*>(&Ks[r][cv * 8]) =
-          r < nk ? *reinterpret_cast<const uint4*>(kc + rix[r] * D + cv * 8) : zero4;
+    if (k0 + BN <= p_last) {
+      issue_tile(stage ^ 1, k0 + BN);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    for (int i = tid; i < BN * (DMAX / 8); i += 128) {   // every column of the tile: unused ones must not hold NaN
-      const int r = i / (DMAX / 8), cv = i - r * (DMAX / 8);
-      *reinterpret_cast<uint4*>(&Vs[r][cv * 8]) =
-          (r < nk && cv < vvec) ? *reinterpret_cast<const uint4*>(vc + rix[r] * Dv + cv * 8) : zero4;
-    }
-    __syncthreads();
+    __syncthreads();   // every thread's copies of this stage have landed
     float s[BN / 8][4];
 #pragma unroll
     for (int nb = 0; nb < BN / 8; ++nb) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
+      for (int ks = 0; ks < KS; ks += 2) {
         if (ks * 16 < D) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ks[nb * 8 + quad][ks * 16 + tq * 2]);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ks[nb * 8 + quad][ks * 16 + tq * 2 + 8]);
-          mma16816<true>(s[nb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+          uint32_t kb[4];
+          ldmatrix_x4(kb, &Ks[stage][nb * 8 + (lane & 7)][ks * 16 + (lane >> 3) * 8]);
+          mma16816<true>(s[nb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[0], kb[1]);
+          if ((ks + 1) * 16 < D)
+            mma16816<true>(s[nb], qa[ks + 1][0], qa[ks + 1][1], qa[ks + 1][2], qa[ks + 1][3], kb[2], kb[3]);
         }
       }
     }
     float mx[2] = {-INFINITY, -INFINITY};
+    if (k0 + BN - 1 <= warp_first && k0 >= warp_lo) {
 #pragma unroll
-    for (int nb = 0; nb < BN / 8; ++nb) {
+      for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int pj = k0 + nb * 8 + tq * 2 + (e & 1);
-        const int pi = (e & 2) ? pi_hi : pi_lo;
-        const int lo_i = (e & 2) ? lo_hi : lo_lo;
-        const bool ok = ((e & 2) ? r_hi : r_lo) < rows && pj <= pi && pj >= lo_i;
-        s[nb][e] = ok ? s[nb][e] * scale - slope * (float)(pi - pj) : -INFINITY;
-        mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
-      }
+        for (int e = 0; e < 4; ++e) {
+          const int pj = k0 + nb * 8 + tq * 2 + (e & 1);
+          s[nb][e] = s[nb][e] * scale2 - slope2 * (float)(((e & 2) ? pi_hi : pi_lo) - pj);
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+        }
+    } else {
+#pragma unroll
+      for (int nb = 0; nb < BN / 8; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int pj = k0 + nb * 8 + tq * 2 + (e & 1);
+          const int pi = (e & 2) ? pi_hi : pi_lo;
+          const int lo_i = (e & 2) ? lo_hi : lo_lo;
+          const bool ok = ((e & 2) ? r_hi : r_lo) < rows && pj <= pi && pj >= lo_i;
+          s[nb][e] = ok ? s[nb][e] * scale2 - slope2 * (float)(pi - pj) : -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+        }
     }
-    float corr[2];
+    float corr[2], mref[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
       const float m_new = fmaxf(m[i], mx[i]);
-      corr[i] = m_new == -INFINITY ? 1.f : __expf(m[i] - m_new);
+      // no key seen so far and none in this tile: nothing to rescale, and a finite stand-in keeps ex2(-inf - m) = 0
+      corr[i] = m_new == -INFINITY ? 1.f : ex2(m[i] - m_new);
+      mref[i] = m_new == -INFINITY ? 0.f : m_new;
       m[i] = m_new;
     }
     float sum[2] = {0.f, 0.f};
@@ -348,7 +405,7 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float p = s[nb][e] == -INFINITY ? 0.f : __expf(s[nb][e] - m[e >> 1]);
+        const float p = ex2(s[nb][e] - mref[e >> 1]);   // masked scores are -inf: ex2 gives 0
         s[nb][e] = p;
         sum[e >> 1] += p;
       }
@@ -375,13 +432,14 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
         for (int nb = 0; nb < NV; nb += 2) {
           if (nb * 8 < Dv) {
             uint32_t vb[4];
-            ldmatrix_x4_trans(vb, &Vs[kb * 16 + (lane & 15)][nb * 8 + (lane >> 4) * 8]);
+            ldmatrix_x4_trans(vb, &Vs[stage][kb * 16 + (lane & 15)][nb * 8 + (lane >> 4) * 8]);
             mma16816<true>(o[nb], a0, a1, a2, a3, vb[0], vb[1]);
             mma16816<true>(o[nb + 1], a0, a1, a2, a3, vb[2], vb[3]);
           }
         }
       }
     }
+    __syncthreads();   // the stage is free for the copy the next pass issues
   }
   const float inv[2] = {l[0] > 0.f ? 1.0f / l[0] : 0.f, l[1] > 0.f ? 1.0f / l[1] : 0.f};
 #pragma unroll
@@ -396,6 +454,21 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
             pack2<true>(o[nb][2] * inv[1], o[nb][3] * inv[1]);
     }
   }
+}
+
+template <int DMAX>
+int launch_varlen_mma(const void* q, const PagedKV& c, const int32_t* cu_q, const int32_t* seq_start, const int32_t* bm,
+                      const float* slopes, int chunk, float sink, float scale, void* out, int B, int max_new, int H,
+                      int G, int D, int Dv, cudaStream_t st) {
+  static std::atomic<uint64_t> mask{0};
+  const int smem = 4 * 64 * (DMAX + 8) * 2;
+  auto kern = bias_attn_varlen_mma_kernel<DMAX>;
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), smem, mask));
+  dim3 grid(cdiv(max_new, BM), B, H);
+  kern<<<grid, 128, smem, st>>>(static_cast<const __nv_bfloat16*>(q), c, cu_q, seq_start, bm, slopes, chunk, sink,
+                                scale, static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -498,6 +571,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
 // - with more than one split - by bias_attn_decode_merge_kernel from a workspace of (max, sum, values) records.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kDecTile = 4;   // query heads per CTA
+// scores are kept in log2 units (log2(e) folded into the query scale and the slopes), so every exponential of the
+// split and merge kernels is one ex2.approx
+constexpr float kLog2e = 1.4426950408889634f;
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float* v);
@@ -549,11 +625,11 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
   const int k_begin = lo + split * per, k_end = min(pi + 1, k_begin + per);
   for (int i = tid; i < kDecTile * D; i += 128) {
     const int r = i / D, d = i - r * D;
-    qs[r][d] = r < nr ? to_f<T>(q[((int64_t)b * H + h0 + r) * D + d]) * scale : 0.f;
+    qs[r][d] = r < nr ? to_f<T>(q[((int64_t)b * H + h0 + r) * D + d]) * (scale * kLog2e) : 0.f;
   }
   float slope[kDecTile];
 #pragma unroll
-  for (int r = 0; r < kDecTile; ++r) slope[r] = (slopes && r < nr) ? slopes[h0 + r] : 0.f;
+  for (int r = 0; r < kDecTile; ++r) slope[r] = (slopes && r < nr) ? slopes[h0 + r] * kLog2e : 0.f;
   __syncthreads();
   const T* kc = static_cast<const T*>(c.k);
   const T* vc = static_cast<const T*>(c.v);
@@ -636,13 +712,13 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
         v += __shfl_xor_sync(gmask, v, 1);
         v -= slope[r] * dist;
         if (v > m[r]) {   // the same for the 8 lanes of the group
-          const float corr = expf(m[r] - v);
+          const float corr = ex2(m[r] - v);
           l[r] *= corr;
 #pragma unroll
           for (int e = 0; e < CH * 8; ++e) acc[r][e] *= corr;
           m[r] = v;
         }
-        p[r] = expf(v - m[r]);
+        p[r] = ex2(v - m[r]);
         l[r] += p[r];
       }
 #pragma unroll
@@ -661,8 +737,8 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
       const float mo = __shfl_xor_sync(0xffffffffu, m[r], o);
       const float lo_ = __shfl_xor_sync(0xffffffffu, l[r], o);
       const float mn = fmaxf(m[r], mo);
-      const float fa = m[r] == -INFINITY ? 0.f : expf(m[r] - mn);
-      const float fb = mo == -INFINITY ? 0.f : expf(mo - mn);
+      const float fa = m[r] == -INFINITY ? 0.f : ex2(m[r] - mn);
+      const float fb = mo == -INFINITY ? 0.f : ex2(mo - mn);
       l[r] = l[r] * fa + lo_ * fb;
 #pragma unroll
       for (int e = 0; e < CH * 8; ++e) {
@@ -691,12 +767,12 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
     float mm = (splits == 1 && sink > 0.f) ? 0.f : -INFINITY;
 #pragma unroll
     for (int w = 0; w < 4; ++w) mm = fmaxf(mm, st[w][r][0]);
-    float ll = (splits == 1 && sink > 0.f) ? sink * expf(0.f - mm) : 0.f, a = 0.f;
+    float ll = (splits == 1 && sink > 0.f) ? sink * ex2(0.f - mm) : 0.f, a = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = st[w][r][0];
       if (mw == -INFINITY) continue;
-      const float f = expf(mw - mm);
+      const float f = ex2(mw - mm);
       ll += st[w][r][1] * f;
       a += st[w][r][2 + d] * f;
     }
@@ -718,14 +794,14 @@ __global__ void __launch_bounds__(128) bias_attn_decode_merge_kernel(const float
   const float* p = part + bh * splits * rec;
   float mm = sink > 0.f ? 0.f : -INFINITY;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[s * rec]);
-  float ll = sink > 0.f ? sink * expf(0.f - mm) : 0.f;
+  float ll = sink > 0.f ? sink * ex2(0.f - mm) : 0.f;
   for (int s = 0; s < splits; ++s)
-    if (p[s * rec] != -INFINITY) ll += p[s * rec + 1] * expf(p[s * rec] - mm);
+    if (p[s * rec] != -INFINITY) ll += p[s * rec + 1] * ex2(p[s * rec] - mm);
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
   for (int d = threadIdx.x; d < Dv; d += 128) {
     float a = 0.f;
     for (int s = 0; s < splits; ++s)
-      if (p[s * rec] != -INFINITY) a += p[s * rec + 2 + d] * expf(p[s * rec] - mm);
+      if (p[s * rec] != -INFINITY) a += p[s * rec + 2 + d] * ex2(p[s * rec] - mm);
     out[bh * Dv + d] = from_f<T>(a * inv);
   }
 }
@@ -802,7 +878,7 @@ extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const flo
   if (T == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(qkv && positions && token_slot && q_out && k_cache && v_cache && page_table && check_dtype(dtype));
   auto st = static_cast<cudaStream_t>(stream);
-  PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
   if (dtype == CVLLM_BF16)
     qknorm_store_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(
         static_cast<const __nv_bfloat16*>(qkv), qkv_stride, q_weight, k_weight, eps, positions, token_slot,
@@ -829,7 +905,7 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
                   check_dtype(dtype) && page_size > 0);
   CVLLM_CHECK_SUPPORTED(Dv <= 256 && B <= 65535 && H <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
-  PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
   const int dvc = cdiv(Dv, 16);
   const float fs = sink ? 1.f : 0.f;
   const size_t cap = 226 * 1024;  // + the static row-index array
@@ -840,17 +916,11 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
   return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B, \
                              max_new, H, G, D, Dv, st)
   if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && !test_options().bias_attn_fma.load()) {
-    dim3 grid(cdiv(max_new, BM), B, H);
     if (D <= 64 && Dv <= 64)
-      bias_attn_varlen_mma_kernel<64><<<grid, 128, 0, st>>>(
-          static_cast<const __nv_bfloat16*>(q), c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale,
-          static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
-    else
-      bias_attn_varlen_mma_kernel<128><<<grid, 128, 0, st>>>(
-          static_cast<const __nv_bfloat16*>(q), c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale,
-          static_cast<__nv_bfloat16*>(out), H, G, D, Dv);
-    CVLLM_CHECK_LAUNCH();
-    return CVLLM_OK;
+      return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B,
+                                   max_new, H, G, D, Dv, st);
+    return launch_varlen_mma<128>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B,
+                                  max_new, H, G, D, Dv, st);
   }
   if (dtype == CVLLM_BF16) {
     if (bn == 64) CVLLM_GO(__nv_bfloat16, 64);
@@ -873,7 +943,7 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
                   page_size > 0);
   CVLLM_CHECK_SUPPORTED(Dv <= 32 * kDecCols && H <= 65535 && B <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
-  PagedKV c{k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size};
+  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
   if (D % 8 == 0 && Dv % 8 == 0 && D <= 256 && Dv <= 256) {
     if (splits > 1) {
       CVLLM_CHECK_ARG(workspace != nullptr);
