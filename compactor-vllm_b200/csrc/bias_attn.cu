@@ -352,12 +352,15 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     __syncthreads();   // every thread's copies of this stage have landed
     float s[BN / 8][4];
 #pragma unroll
-    for (int nb = 0; nb < BN / 8; ++nb) {
+    for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
+    // k-steps outside, key blocks inside: eight independent accumulator chains are in flight per k-step
 #pragma unroll
-      for (int ks = 0; ks < KS; ks += 2) {
-        if (ks * 16 < D) {
+    for (int ks = 0; ks < KS; ks += 2) {
+      if (ks * 16 < D) {
+#pragma unroll
+        for (int nb = 0; nb < BN / 8; ++nb) {
           uint32_t kb[4];
           ldmatrix_x4(kb, &Ks[stage][nb * 8 + (lane & 7)][ks * 16 + (lane >> 3) * 8]);
           mma16816<true>(s[nb], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kb[0], kb[1]);
@@ -570,6 +573,10 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
 // running softmax state.  The states are merged by shuffles inside a warp, through shared memory across warps, and
 // - with more than one split - by bias_attn_decode_merge_kernel from a workspace of (max, sum, values) records.
 // ---------------------------------------------------------------------------------------------------------
+// largest CH (64-column chunks of the head size) whose query slice the decode kernel keeps in registers
+#ifndef CVLLM_DEC_QREG_CH
+#define CVLLM_DEC_QREG_CH 2
+#endif
 constexpr int kDecTile = 4;   // query heads per CTA
 // scores are kept in log2 units (log2(e) folded into the query scale and the slopes), so every exponential of the
 // split and merge kernels is one ex2.approx
@@ -643,7 +650,7 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
   }
   const unsigned gmask = 0xffu << (tid & 24);   // the group's own lanes: groups of a warp leave the loop apart
   // the lane's slice of the tile's queries stays in registers when it is small enough (D <= 128)
-  constexpr bool kQInRegs = CH <= 2;
+  constexpr bool kQInRegs = CH <= CVLLM_DEC_QREG_CH;
   float qr[kQInRegs ? kDecTile : 1][kQInRegs ? CH * 8 : 1];
   if constexpr (kQInRegs) {
 #pragma unroll
