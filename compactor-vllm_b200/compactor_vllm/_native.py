@@ -85,7 +85,7 @@ _SIGNATURES = {
     "cvllm_qknorm_store": (_i, [_p, _i64, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
                                 _i, _i, _i, _i, _i, _i, _i, _p]),
     "cvllm_bias_attn_varlen": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _f, _p,
-                                    _i, _i, _i, _i, _i, _i, _i, _p]),
+                                    _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _p]),
     "cvllm_bias_attn_decode": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _i, _i, _f, _p,
                                     _i, _i, _i, _i, _i, _i, _i, _p, _sz, _i, _p]),
 }

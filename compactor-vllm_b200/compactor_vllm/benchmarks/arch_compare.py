@@ -197,7 +197,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
         N.check(lib.cvllm_bias_attn_varlen(N.ptr(q), N.ptr(attn.k_cache), N.ptr(attn.v_cache), *table,
                                            N.ptr(c.cu_seqlens_q), N.ptr(c.seq_start), N.ptr(c.batch_mapping),
                                            N.ptr(attn.slopes), attn.chunk, 1, attn.scale, N.ptr(out), 1, L, H, G, D, D,
-                                           code, N.stream(dev)), "varlen")
+                                           L, attn.k_cache.shape[0], pt.shape[-1], code, N.stream(dev)), "varlen")
 
     prefill_ctx(0)
     add("qknorm_store", timed(store), nbytes=2 * L * ((H + 2 * G) * D + (H + 2 * G) * D),

@@ -177,8 +177,8 @@ class BiasedChunkAttention(nn.Module):
             N.check(lib.cvllm_bias_attn_varlen(
                 N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache), *table, N.ptr(ctx.cu_seqlens_q),
                 N.ptr(ctx.seq_start), N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink),
-                self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, code, N.stream(dev)),
-                "cvllm_bias_attn_varlen")
+                self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, T, self.k_cache.shape[0], pt.shape[-1],
+                code, N.stream(dev)), "cvllm_bias_attn_varlen")
         else:
             assert ctx.batch_mapping.numel() == T
             splits = self.decode_splits(T, int(ctx.max_seqlen_k))

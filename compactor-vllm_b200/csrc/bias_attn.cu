@@ -874,6 +874,13 @@ int dispatch_dvc(int dvc, const void* q, const PagedKV& c, const int32_t* cu_q, 
 
 using namespace cvllm;
 
+// prefill_attn_bias.cu: the tcgen05 / TMEM / TMA pipeline for 16-bit storage, D = Dv = 128, pages of a multiple of 128
+// rows and an even number of query heads per KV head
+int cvllm_launch_prefill_bias(const void* q, const void* k_cache, const void* v_cache, int64_t cache_rows, void* out,
+                              const int32_t* seq_start, const float* slopes, const int32_t* page_table,
+                              const int32_t* batch_mapping, const int32_t* cu_seqlens_q, int B, int N, int HQ, int HKV,
+                              int PS, int NLP, int max_seqlen_q, float scale, int chunk, int sink, cudaStream_t st);
+
 static int check_dtype(int dtype) { return dtype == CVLLM_BF16 || dtype == CVLLM_F32; }
 
 extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weight, const float* k_weight,
@@ -905,7 +912,8 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
                                       int page_size, const int32_t* cu_seqlens_q, const int32_t* seq_start,
                                       const int32_t* batch_mapping, const float* slopes, int chunk, int sink,
                                       float scale, void* out, int B, int max_new, int H, int G, int D, int Dv,
-                                      int dtype, cvllm_stream_t stream) {
+                                      int total_tokens, int64_t cache_rows, int pages_per_head, int dtype,
+                                      cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && cu_seqlens_q && seq_start && batch_mapping && out &&
@@ -922,7 +930,13 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
 #define CVLLM_GO(T, BN) \
   return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B, \
                              max_new, H, G, D, Dv, st)
-  if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && !test_options().bias_attn_fma.load()) {
+  const int path = test_options().bias_attn_fma.load();   // 0 product, 1 fp32 FMA kernel, 2 no tcgen05 kernel
+  if (dtype == CVLLM_BF16 && D == 128 && Dv == 128 && page_size % 128 == 0 && (H / G) % 2 == 0 && path == 0 &&
+      table_stride_head == pages_per_head && table_stride_slot == (int64_t)G * pages_per_head && cache_rows > 0)
+    return cvllm_launch_prefill_bias(q, k_cache, v_cache, cache_rows, out, seq_start, slopes, page_table,
+                                     batch_mapping, cu_seqlens_q, B, total_tokens, H, G, page_size, pages_per_head,
+                                     max_new, scale, chunk, sink, st);
+  if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && path != 1) {
     if (D <= 64 && Dv <= 64)
       return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B,
                                    max_new, H, G, D, Dv, st);

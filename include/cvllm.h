@@ -66,7 +66,8 @@ uint64_t cvllm_launch_count(void);
  *   "grs_rows_per_round" r   rows per reduce round of cvllm_gemm_allreduce (multiple of 256; 0 = default 256)
  *   "grs_probe" mask         timing probes of cvllm_gemm_allreduce (results are wrong on purpose: 1 no TMA loads,
  *                            2 no UMMA, 4 no stores, 8 no reduce, 16 no L2 hints)
- *   "bias_attn_fma" 1|0      bfloat16 portions of cvllm_bias_attn_varlen on the fp32 FMA kernel instead of mma.sync (A/B)
+ *   "bias_attn_fma" 0|1|2    bfloat16 portions of cvllm_bias_attn_varlen: 0 product choice, 1 the fp32 FMA kernel,
+ *                            2 mma.sync also where the tcgen05 kernel would serve (A/B)
  *   "grs_debug_host_ptr" p   pinned host buffer (64 words per CTA) for cvllm_gemm_allreduce's timeout records
  * Returns CVLLM_E_ARG for an unknown name. */
 int cvllm_set_test_option(const char* name, double value);
@@ -456,12 +457,16 @@ int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weigh
 
 /* Portions: sequence b brings tokens cu_seqlens_q[b] .. cu_seqlens_q[b+1]-1 at positions seq_start[b] + 0, 1, ...;
  * all their keys (and every earlier one) are in the cache of slot batch_mapping[b].  out [T, H, Dv].
- * max_new = the largest number of new tokens of one sequence.  Dv <= 256. */
+ * max_new = the largest number of new tokens of one sequence, total_tokens = T, cache_rows = rows of k_cache,
+ * pages_per_head = the page table's last dimension.  Dv <= 256.
+ * Kernels: tcgen05 / TMEM / TMA (bfloat16, D = Dv = 128, page_size % 128 == 0, H / G even, dense page table);
+ * mma.sync (bfloat16, D % 16 == 0, Dv % 8 == 0, both <= 128); fp32 FMA (everything else, float32 included). */
 int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
                            int64_t table_stride_slot, int64_t table_stride_head, int page_size,
                            const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* batch_mapping,
                            const float* slopes, int chunk, int sink, float scale, void* out, int B, int max_new,
-                           int H, int G, int D, int Dv, int dtype, cvllm_stream_t stream);
+                           int H, int G, int D, int Dv, int total_tokens, int64_t cache_rows, int pages_per_head,
+                           int dtype, cvllm_stream_t stream);
 
 /* Decode: one query per sequence at position positions[b] (its key is in the cache already).  q [B, H, D],
  * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 256.  With D and Dv multiples of 8 (and D <= 256) the keys

@@ -574,6 +574,56 @@ def test_bfloat16_portions_on_tensor_cores(dim, vdim, chunk):
         assert row_errs(mma[i], fma[i]).median() < 0.01
 
 
+@pytest.mark.parametrize("chunk", [0, 128, 200, 37])
+def test_bfloat16_portions_on_the_tcgen05_pipeline(chunk):
+    """Key and value size 128, pages of 128 rows, two query heads per KV head: portions run on the tcgen05 kernel.
+    Checked against the oracle and against the mma.sync and FMA kernels on the same inputs; the portions start and
+    end off the 128-row tiles, and the chunk edges fall inside tiles."""
+    from compactor_vllm import _native as N
+    from oracle import movolorn as O
+
+    cfg = {"architecture": "Movolorn", "vocab": 80, "width": 64, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+           "layers": [{"type": "attention", "mixer": attn_cfg(4, 2, 128, 128, chunk), "mlp": {"kind": "dense", "ff": 64}},
+                      {"type": "attention", "mixer": attn_cfg(2, 1, 128, 128, chunk), "mlp": None}]}
+    r = make_runner(cfg, "bfloat16", pages=8, page_size=128)
+    om = oracle_model(r.model)
+    reqs = [tokens(420, 80, 60), tokens(131, 80, 61)]
+    want = [O.forward(om, t) for t in reqs]
+
+    def run():
+        seqs, got, at = [new_seq(), new_seq()], [[], []], [0, 0]
+        for step in ([(0, 70), (1, 3)], [(0, 200), (1, 128)], [(0, 1)], [(0, 149)]):
+            entries, spans, base = [], [], 0
+            for i, n in step:
+                part = reqs[i][at[i]:at[i] + n]
+                seqs[i].prompt_token_ids.extend(part)
+                entries.append((seqs[i], part))
+                spans.append((i, base, len(part)))
+                at[i] += len(part)
+                base += len(part)
+            logits = r.run_step(entries, rows=list(range(base)))
+            for i, b_, n in spans:
+                got[i].append(logits[b_:b_ + n])
+        r.release(seqs)
+        return [torch.cat(g_).float().cpu() for g_ in got]
+
+    launches = N.lib().cvllm_launch_count()
+    umma = run()
+    assert N.lib().cvllm_launch_count() > launches
+    outs = {}
+    for option in (2, 1):
+        N.set_test_option("bias_attn_fma", option)
+        try:
+            outs[option] = run()
+        finally:
+            N.set_test_option("bias_attn_fma", 0)
+    for i in range(2):
+        assert close(umma[i], want[i], "bfloat16"), i
+        for option in (2, 1):
+            assert close(outs[option][i], want[i], "bfloat16")
+            assert row_errs(umma[i], outs[option][i]).median() < 0.01 and rel_err(umma[i], outs[option][i]) < 0.05
+
+
 # ------------------------------------------------------------------------------ generation through the entry point
 def test_greedy_generation_through_llm_generate():
     """`LLM.generate` with the step scheduler: prompts in portions of at most 16 tokens beside decoding requests, five
