@@ -662,80 +662,110 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
         for (int e = 0; e < 8; ++e) qr[r][i * 8 + e] = cb < D ? qs[r][cb + e] : 0.f;
       }
   }
-  // two keys of the group per pass (j and j + 16): the loads of both are in flight before either is used
-  for (int j = k_begin + gid; j < k_end; j += 32) {
-    const bool two = j + 16 < k_end;
-    const int64_t row[2] = {cache_row(c, slot, g, j), two ? cache_row(c, slot, g, j + 16) : 0};
-    float kv[2][CH][8];
-#pragma unroll
-    for (int u = 0; u < 2; ++u)
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int cb = (sub + 8 * i) * 8;
-        if (cb < D && (u == 0 || two)) load8<T>(kc + row[u] * D + cb, kv[u][i]);
-        else
-#pragma unroll
-          for (int e = 0; e < 8; ++e) kv[u][i][e] = 0.f;
-      }
-    float vv[2][CH][8];
-#pragma unroll
-    for (int u = 0; u < 2; ++u)
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int cb = (sub + 8 * i) * 8;
-        if (cb < Dv && (u == 0 || two)) load8<T>(vc + row[u] * Dv + cb, vv[u][i]);
-        else
-#pragma unroll
-          for (int e = 0; e < 8; ++e) vv[u][i][e] = 0.f;
-      }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      if (u == 1 && !two) break;
-      float s[kDecTile];
-#pragma unroll
-      for (int r = 0; r < kDecTile; ++r) s[r] = 0.f;
+  // Each lane streams ITS slices of the group's key and value rows through a ring of kStages entries in shared
+  // memory with cp.async: kStages keys are in flight per group whatever the register budget, and a lane only ever
+  // reads what it copied itself, so the ring needs no barrier - cp.async.wait_group orders a lane's own copies.
+  // Entry layout [stage][K chunks | V chunks][thread]: consecutive lanes hit consecutive 16-byte words.
+  constexpr int kStages = CH <= 2 ? 4 : 2;
+  constexpr int kVec = 16 / sizeof(T);          // elements per 16-byte piece
+  constexpr int kPieces = 8 / kVec;             // 16-byte pieces per 8-element chunk (1 for 16 bit, 2 for 32 bit)
+  extern __shared__ __align__(16) unsigned char ring_raw[];
+  uint4* ring = reinterpret_cast<uint4*>(ring_raw);
+  auto ring_at = [&](int stage, int which, int i, int piece) -> uint4* {
+    return ring + ((((stage * 2 + which) * CH + i) * kPieces + piece) * 128 + tid);
+  };
+  const int n_mine = k_end > k_begin + gid ? (k_end - k_begin - gid + 15) / 16 : 0;
+  auto issue = [&](int t) {
+    if (t < n_mine) {
+      const int64_t row = cache_row(c, slot, g, k_begin + gid + 16 * t);
+      const int stage = t % kStages;
 #pragma unroll
       for (int i = 0; i < CH; ++i) {
         const int cb = (sub + 8 * i) * 8;
-        if (cb < D) {
 #pragma unroll
-          for (int r = 0; r < kDecTile; ++r)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float qv;
-              if constexpr (kQInRegs) qv = qr[r][i * 8 + e];
-              else qv = qs[r][cb + e];
-              s[r] = fmaf(qv, kv[u][i][e], s[r]);
-            }
+        for (int pc = 0; pc < kPieces; ++pc) {
+          if (cb < D) cp_async16(ring_at(stage, 0, i, pc), kc + row * D + cb + pc * kVec, 16);
+          if (cb < Dv) cp_async16(ring_at(stage, 1, i, pc), vc + row * Dv + cb + pc * kVec, 16);
         }
       }
-      const float dist = (float)(pi - (j + 16 * u));
-      float p[kDecTile];
+    }
+    cp_async_commit();   // also when empty: the group count per pass stays the same
+  };
+  auto read8 = [&](int stage, int which, int i, float* v) {
+    if constexpr (sizeof(T) == 2) {
+      const uint4 u = *ring_at(stage, which, i, 0);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-      for (int r = 0; r < kDecTile; ++r) {
-        float v = s[r];
-        v += __shfl_xor_sync(gmask, v, 4);
-        v += __shfl_xor_sync(gmask, v, 2);
-        v += __shfl_xor_sync(gmask, v, 1);
-        v -= slope[r] * dist;
-        if (v > m[r]) {   // the same for the 8 lanes of the group
-          const float corr = ex2(m[r] - v);
-          l[r] *= corr;
-#pragma unroll
-          for (int e = 0; e < CH * 8; ++e) acc[r][e] *= corr;
-          m[r] = v;
-        }
-        p[r] = ex2(v - m[r]);
-        l[r] += p[r];
+      for (int k = 0; k < 4; ++k) {
+        v[2 * k] = __uint_as_float(w[k] << 16);
+        v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
       }
+    } else {
+      const uint4 a = *ring_at(stage, which, i, 0), b2 = *ring_at(stage, which, i, kPieces - 1);
+      v[0] = __uint_as_float(a.x); v[1] = __uint_as_float(a.y); v[2] = __uint_as_float(a.z); v[3] = __uint_as_float(a.w);
+      v[4] = __uint_as_float(b2.x); v[5] = __uint_as_float(b2.y); v[6] = __uint_as_float(b2.z); v[7] = __uint_as_float(b2.w);
+    }
+  };
 #pragma unroll
-      for (int i = 0; i < CH; ++i)
+  for (int t = 0; t < kStages - 1; ++t) issue(t);
+  for (int t = 0; t < n_mine; ++t) {
+    issue(t + kStages - 1);          // refills the entry the previous pass has finished reading
+    cp_async_wait<kStages - 1>();    // everything but the newest kStages - 1 groups has landed: key t is here
+    const int stage = t % kStages;
+    const int j = k_begin + gid + 16 * t;
+    float s[kDecTile];
+#pragma unroll
+    for (int r = 0; r < kDecTile; ++r) s[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int cb = (sub + 8 * i) * 8;
+      if (cb < D) {
+        float kv[8];
+        read8(stage, 0, i, kv);
 #pragma unroll
         for (int r = 0; r < kDecTile; ++r)
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[r][i * 8 + e] = fmaf(p[r], vv[u][i][e], acc[r][i * 8 + e]);
+          for (int e = 0; e < 8; ++e) {
+            float qv;
+            if constexpr (kQInRegs) qv = qr[r][i * 8 + e];
+            else qv = qs[r][cb + e];
+            s[r] = fmaf(qv, kv[e], s[r]);
+          }
+      }
+    }
+    const float dist = (float)(pi - j);
+    float p[kDecTile];
+#pragma unroll
+    for (int r = 0; r < kDecTile; ++r) {
+      float v = s[r];
+      v += __shfl_xor_sync(gmask, v, 4);
+      v += __shfl_xor_sync(gmask, v, 2);
+      v += __shfl_xor_sync(gmask, v, 1);
+      v -= slope[r] * dist;
+      if (v > m[r]) {   // the same for the 8 lanes of the group
+        const float corr = ex2(m[r] - v);
+        l[r] *= corr;
+#pragma unroll
+        for (int e = 0; e < CH * 8; ++e) acc[r][e] *= corr;
+        m[r] = v;
+      }
+      p[r] = ex2(v - m[r]);
+      l[r] += p[r];
+    }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int cb = (sub + 8 * i) * 8;
+      if (cb < Dv) {
+        float vv[8];
+        read8(stage, 1, i, vv);
+#pragma unroll
+        for (int r = 0; r < kDecTile; ++r)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[r][i * 8 + e] = fmaf(p[r], vv[e], acc[r][i * 8 + e]);
+      }
     }
   }
+  cp_async_wait<0>();
   // the four groups of a warp (lanes differing in bits 3 and 4)
 #pragma unroll
   for (int o = 8; o <= 16; o <<= 1) {
@@ -813,6 +843,21 @@ __global__ void __launch_bounds__(128) bias_attn_decode_merge_kernel(const float
   }
 }
 
+template <typename T, int CH>
+int launch_decode_split_ch(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
+                           const float* slopes, int chunk, float sink, float scale, void* out, float* part, dim3 grid,
+                           int H, int G, int D, int Dv, int splits, int reserved_slot, cudaStream_t st) {
+  // the ring: stages x (K | V) x CH chunks x 16-byte pieces per chunk x 128 threads x 16 bytes
+  const size_t ring = (size_t)(CH <= 2 ? 4 : 2) * 2 * CH * (8 / (16 / sizeof(T))) * 128 * 16;
+  static std::atomic<uint64_t> mask{0};
+  auto kern = bias_attn_decode_split_kernel<T, CH>;
+  CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)ring, mask));
+  kern<<<grid, 128, ring, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, chunk, sink, scale,
+                                static_cast<T*>(out), part, H, G, D, Dv, splits, reserved_slot);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
 template <typename T>
 int launch_decode_split(const void* q, const PagedKV& c, const int32_t* positions, const int32_t* bm,
                         const float* slopes, int chunk, float sink, float scale, void* out, float* part, int B, int H,
@@ -820,16 +865,16 @@ int launch_decode_split(const void* q, const PagedKV& c, const int32_t* position
   const int R = H / G, tiles = cdiv(R, kDecTile);
   dim3 grid(splits, G * tiles, B);
   const int ch = cdiv(D > Dv ? D : Dv, 64);
-#define CVLLM_GO(CH)                                                                                             \
-  bias_attn_decode_split_kernel<T, CH><<<grid, 128, 0, st>>>(static_cast<const T*>(q), c, positions, bm, slopes, \
-                                                             chunk, sink, scale, static_cast<T*>(out), part, H, G, D, \
-                                                             Dv, splits, reserved_slot)
+  int rc;
+#define CVLLM_GO(CH) \
+  rc = launch_decode_split_ch<T, CH>(q, c, positions, bm, slopes, chunk, sink, scale, out, part, grid, H, G, D, Dv, \
+                                     splits, reserved_slot, st)
   if (ch == 1) CVLLM_GO(1);
   else if (ch == 2) CVLLM_GO(2);
   else if (ch == 3) CVLLM_GO(3);
   else CVLLM_GO(4);
 #undef CVLLM_GO
-  CVLLM_CHECK_LAUNCH();
+  if (rc != CVLLM_OK) return rc;
   if (splits > 1) {
     bias_attn_decode_merge_kernel<T><<<B * H, 128, 0, st>>>(part, sink, static_cast<T*>(out), Dv, splits);
     CVLLM_CHECK_LAUNCH();
