@@ -600,6 +600,64 @@ __device__ __forceinline__ void load8<float>(const float* p, float* v) {
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float* v);
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* v) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack2<true>(v[0], v[1]), pack2<true>(v[2], v[3]), pack2<true>(v[4], v[5]),
+                                            pack2<true>(v[6], v[7]));
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// q / k norm + store with 16-byte accesses: D and Dv multiples of 8 and at most 256, rows 16-byte aligned.
+// LPR lanes (a power of two, 8 elements each) share a head row, so a warp takes 32 / LPR rows at once and a CTA
+// 4 * 32 / LPR; grid = (tokens, row groups): a decode step's few tokens still spread over many CTAs.  A lane keeps its
+// piece of the row in registers between the sum of squares and the scaled write.
+template <typename T>
+__global__ void __launch_bounds__(128) qknorm_store_vec_kernel(
+    const T* __restrict__ qkv, int64_t qkv_stride, const float* __restrict__ q_w, const float* __restrict__ k_w,
+    float eps, const int32_t* __restrict__ positions, const int32_t* __restrict__ token_slot, T* __restrict__ q_out,
+    T* __restrict__ k_cache, T* __restrict__ v_cache, PagedKV c, int32_t* __restrict__ bh_lens, int H, int G, int D,
+    int Dv, int reserved_slot, int lpr) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = token_slot[t];
+  const int pos = positions[t];
+  const T* row = qkv + (int64_t)t * qkv_stride;
+  const int rows_per_warp = 32 / lpr;
+  const int r = (blockIdx.y * 4 + warp) * rows_per_warp + lane / lpr;
+  const int cb = (lane % lpr) * 8;
+  const bool is_q = r < H, is_k = r >= H && r < H + G, is_v = r >= H + G && r < H + 2 * G;
+  const bool stores = slot != reserved_slot;
+  float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if ((is_q || (is_k && stores)) && cb < D) load8<T>(row + (int64_t)r * D + cb, x);
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+  for (int o = lpr >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // every lane takes part
+  if ((is_q || (is_k && stores)) && cb < D) {
+    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+    const float* w = is_q ? q_w : k_w;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = w ? x[e] * inv * w[cb + e] : x[e] * inv;
+    T* dst = is_q ? q_out + ((int64_t)t * H + r) * D : k_cache + cache_row(c, slot, r - H, pos) * D;
+    store8<T>(dst + cb, x);
+  }
+  if (is_v && stores) {
+    const int g = r - H - G;
+    if (cb < Dv) {
+      float v[8];
+      load8<T>(row + (int64_t)(H + G) * D + (int64_t)g * Dv + cb, v);
+      store8<T>(v_cache + cache_row(c, slot, g, pos) * Dv + cb, v);
+    }
+    if (cb == 0 && bh_lens) atomicMax(bh_lens + slot * G + g, pos + 1);
+  }
+}
+
 template <typename T, int CH>
 __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
     const T* __restrict__ q, PagedKV c, const int32_t* __restrict__ positions,
@@ -938,6 +996,28 @@ extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const flo
   CVLLM_CHECK_ARG(qkv && positions && token_slot && q_out && k_cache && v_cache && page_table && check_dtype(dtype));
   auto st = static_cast<cudaStream_t>(stream);
   const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
+  const int64_t align = dtype == CVLLM_BF16 ? 8 : 4;
+  if (D % 8 == 0 && Dv % 8 == 0 && D <= 256 && Dv <= 256 && qkv_stride % align == 0 && aligned16(qkv) &&
+      aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache)) {
+    int lpr = 1;   // lanes per row: the next power of two that covers the longer of the two row sizes
+    while (lpr * 8 < (D > Dv ? D : Dv)) lpr <<= 1;
+    const int rows_per_cta = 4 * (32 / lpr);
+    CVLLM_CHECK_SUPPORTED(T <= 2147483647 && cdiv(H + 2 * G, rows_per_cta) <= 65535);
+    const dim3 grid(T, cdiv(H + 2 * G, rows_per_cta));
+    if (dtype == CVLLM_BF16)
+      qknorm_store_vec_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(qkv), qkv_stride, q_weight, k_weight, eps, positions, token_slot,
+          static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+          static_cast<__nv_bfloat16*>(v_cache), c, bh_lens, H, G, D, Dv, reserved_slot, lpr);
+    else
+      qknorm_store_vec_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(qkv), qkv_stride, q_weight,
+                                                           k_weight, eps, positions, token_slot,
+                                                           static_cast<float*>(q_out), static_cast<float*>(k_cache),
+                                                           static_cast<float*>(v_cache), c, bh_lens, H, G, D, Dv,
+                                                           reserved_slot, lpr);
+    CVLLM_CHECK_LAUNCH();
+    return CVLLM_OK;
+  }
   if (dtype == CVLLM_BF16)
     qknorm_store_kernel<__nv_bfloat16><<<T, 128, 0, st>>>(
         static_cast<const __nv_bfloat16*>(qkv), qkv_stride, q_weight, k_weight, eps, positions, token_slot,
