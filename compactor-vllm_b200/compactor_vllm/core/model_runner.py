@@ -108,6 +108,7 @@ class ModelRunner:
         self.eos = config.eos
         self._graphs: dict = {}
         self._step_graphs: dict = {}
+        self._room: dict = {}          # seq_id -> tokens the pages granted so far can hold (mixed-step models)
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "graph_replays": 0, "bytes_reclaimed": 0, "steps": 0}
 
     # ------------------------------------------------------------------ prefill
@@ -251,28 +252,46 @@ class ModelRunner:
             s.status = SequenceStatus.FINISHED
 
     # -------------------------------------------------------------- mixed steps
+    def _make_room(self, seq: Sequence, tokens: int) -> bool:
+        """Cache room for `tokens` more tokens of a sequence (a slot at its first call).  What the pages already
+        granted can hold is remembered on the host, so a step that stays inside it costs no allocator call and no
+        device round trip - a decoding sequence asks once per page, or never when its whole length was reserved at
+        admission."""
+        need = seq.num_computed_tokens + tokens
+        if need <= self._room.get(seq.seq_id, 0):
+            return True
+        ok, _ = self.kv.allocate_sequences([seq.seq_id], [tokens])
+        if ok:
+            ps = self.kv.page_size
+            self._room[seq.seq_id] = max(self._room.get(seq.seq_id, 0), -(-need // ps) * ps)
+        return ok
+
     @torch.no_grad()
-    def run_step(self, entries: Seq[Tuple[Sequence, Seq[int]]], rows: Optional[Seq[int]] = None) -> torch.Tensor:
+    def run_step(self, entries: Seq[Tuple[Sequence, Seq[int]]], rows: Optional[Seq[int]] = None,
+                 temperatures: Optional[Seq[float]] = None) -> torch.Tensor:
         """One forward pass over a mixed batch: every entry is (sequence, its next tokens) — a portion of a prompt
         or a single decoded token — continuing from what earlier steps left in the cache.  Returns the logits of
-        `rows` (indices into the step's packed tokens; None = the last token of every entry).  Room for the new
-        tokens is reserved here; a sequence gets its cache slot at its first entry.  Models with `mixed_steps`."""
+        `rows` (indices into the step's packed tokens; None = the last token of every entry), or — with
+        `temperatures`, one per entry — the token sampled after every entry's last token.  Room for the new tokens
+        is reserved here; a sequence gets its cache slot at its first entry.  Models with `mixed_steps`."""
         assert self.mixed_steps, "this model runs whole prompts and single tokens only"
+        assert rows is None or temperatures is None
         dev = self.device
         lens = [len(t) for _, t in entries]
         assert lens and min(lens) > 0
         starts = [s.num_computed_tokens for s, _ in entries]
-        ok, batch_mapping = self.kv.allocate_sequences([s.seq_id for s, _ in entries], lens)
-        if not ok:
-            raise KVCacheExhausted(f"no room for a step of {sum(lens)} tokens ({self.kv.num_free_tokens} tokens free)")
+        for (s, _), n in zip(entries, lens):
+            if not self._make_room(s, n):
+                raise KVCacheExhausted(f"no room for {n} more tokens of sequence {s.seq_id} "
+                                       f"({self.kv.num_free_tokens} tokens free)")
         T = sum(lens)
         if max(lens) == 1 and not self.config.enforce_eager:
-            logits = self._graph_decode_step(entries, starts, rows)
+            out = self._graph_decode_step(entries, starts, rows, temperatures)
             for s, _ in entries:
                 s.num_computed_tokens += 1
             self.stats["steps"] += 1
             self.stats["graph_replays"] += 1
-            return logits
+            return out
         # one host->device copy for all the step's index vectors
         pos = [p for st, n in zip(starts, lens) for p in range(st, st + n)]
         slot_of = [self.kv.seq_id_to_batch[s.seq_id] for s, _ in entries]
@@ -280,10 +299,12 @@ class ModelRunner:
         for n in lens:
             cu.append(cu[-1] + n)
         packed = torch.tensor([t for _, toks in entries for t in toks] + pos
-                              + [sl for sl, n in zip(slot_of, lens) for _ in range(n)] + cu + starts,
+                              + [sl for sl, n in zip(slot_of, lens) for _ in range(n)] + cu + starts + slot_of,
                               dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
         ids, positions, token_slot = packed[:T].long(), packed[T:2 * T], packed[2 * T:3 * T]
-        cu_t, start_t = packed[3 * T:3 * T + len(cu)], packed[3 * T + len(cu):]
+        B = len(entries)
+        cu_t, start_t = packed[3 * T:3 * T + B + 1], packed[3 * T + B + 1:3 * T + 2 * B + 1]
+        batch_mapping = packed[3 * T + 2 * B + 1:]
         set_context(is_prefill=max(lens) > 1, cu_seqlens_q=cu_t, cu_seqlens_k=cu_t, max_seqlen_q=max(lens),
                     max_seqlen_k=max(st + n for st, n in zip(starts, lens)), batch_mapping=batch_mapping,
                     positions_i32=positions, token_slot=token_slot, seq_start=start_t)
@@ -295,30 +316,33 @@ class ModelRunner:
             s.num_computed_tokens += n
         self.stats["steps"] += 1
         self.stats["prefill_tokens"] += sum(n for n in lens if n > 1)
+        if temperatures is not None:
+            return self.sampler(logits, torch.tensor(list(temperatures), dtype=torch.float32, device=dev))
         return logits
 
-    def _graph_decode_step(self, entries, starts, rows) -> torch.Tensor:
+    def _graph_decode_step(self, entries, starts, rows, temperatures=None) -> torch.Tensor:
         """A step of single tokens as a CUDA-graph replay (one graph per padded batch size; padding rows sit on the
-        reserved slot, store nothing and attend to nothing).  The graph holds the whole forward pass and the logits of
-        every row; ids, positions and slots are copied into its static buffer before the replay."""
+        reserved slot, store nothing and attend to nothing).  The graph holds the whole forward pass, the logits of
+        every row and the sampler on them; ids, positions, slots and temperatures are copied into its static buffer
+        before the replay.  Returns logits rows, or the sampled tokens when temperatures are given."""
         dev = self.device
         B = len(entries)
         bs = _pad_batch(B)
         g = self._step_graphs.get(bs)
         if g is None:
-            st = {"packed": torch.zeros(3 * bs, dtype=torch.int32, device=dev)}
-            st["packed"][2 * bs:] = RESERVED_BATCH
+            st = {"packed": torch.zeros(4 * bs, dtype=torch.int32, device=dev)}   # ids, positions, slots, temperatures
+            st["packed"][2 * bs:3 * bs] = RESERVED_BATCH
 
             def forward():
                 pk = st["packed"]
-                ids, pos, slots = pk[:bs].long(), pk[bs:2 * bs], pk[2 * bs:]
+                ids, pos, slots = pk[:bs].long(), pk[bs:2 * bs], pk[2 * bs:3 * bs]
                 # max_seqlen_k: the replay serves any context length, so the key splits are sized for the longest
                 set_context(is_prefill=False, batch_mapping=slots, positions_i32=pos, token_slot=slots,
                             max_seqlen_q=1, max_seqlen_k=self.config.max_model_len)
                 hidden = self.model(ids, pos.long())
                 out = self.model.lm_head(hidden)
                 reset_context()
-                return out
+                return out, self.sampler(out, pk[3 * bs:].view(torch.float32))
 
             side = torch.cuda.Stream(device=dev)
             side.wait_stream(torch.cuda.current_stream())
@@ -327,21 +351,28 @@ class ModelRunner:
                 side.synchronize()
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=side):
-                    st["logits"] = forward()
+                    st["logits"], st["tokens"] = forward()
             torch.cuda.current_stream().wait_stream(side)
             g = self._step_graphs[bs] = (graph, st)
         graph, st = g
         pad = bs - B
         slot_of = [self.kv.seq_id_to_batch[s.seq_id] for s, _ in entries]
         host = torch.tensor([toks[0] for _, toks in entries] + [0] * pad + list(starts) + [0] * pad
-                            + slot_of + [RESERVED_BATCH] * pad, dtype=torch.int32).pin_memory()
-        st["packed"].copy_(host, non_blocking=True)
+                            + slot_of + [RESERVED_BATCH] * pad, dtype=torch.int32)
+        if temperatures is not None:   # the fourth quarter of the buffer holds fp32 bit patterns
+            temps = torch.tensor(list(temperatures) + [0.0] * pad, dtype=torch.float32).view(torch.int32)
+            host = torch.cat([host, temps])
+        st["packed"][:host.numel()].copy_(host.pin_memory(), non_blocking=True)
         graph.replay()
+        if temperatures is not None:
+            return st["tokens"][:B]
         pick = list(range(B)) if rows is None else list(rows)
         return st["logits"].index_select(0, torch.tensor(pick, dtype=torch.int64, device=dev))
 
     def release(self, seqs: Seq[Sequence]) -> None:
         """Give back the slots and pages of finished sequences."""
+        for s in seqs:
+            self._room.pop(s.seq_id, None)
         self.kv.free_sequences([s.seq_id for s in seqs])
 
     @torch.no_grad()
@@ -359,8 +390,7 @@ class ModelRunner:
                 need = min(n + s.sampling_params.max_new_tokens, self.config.max_model_len)
                 if need > self.kv.num_free_tokens:
                     break
-                ok, _ = self.kv.allocate_sequences([s.seq_id], [need])
-                assert ok
+                assert self._make_room(s, need)
                 s.status = SequenceStatus.RUNNING
                 running.append(waiting.popleft())
             if not running:
@@ -376,13 +406,12 @@ class ModelRunner:
                     n = min(s.num_prompt_tokens - done, left)
                     entries.append((s, s.prompt_token_ids[done:done + n]))
                     left -= n
-            logits = self.run_step(entries)
-            sampled = [i for i, (s, _) in enumerate(entries) if s.num_computed_tokens >= s.num_prompt_tokens]
-            if sampled:
-                temps = torch.tensor([entries[i][0].sampling_params.temperature for i in sampled], device=self.device)
-                toks = self.sampler(logits[torch.tensor(sampled, device=self.device)], temps).tolist()
-                for i, t in zip(sampled, toks):
-                    self._accept(entries[i][0], t)
+            # every entry gets a token sampled after its last position (in the graph for single-token steps); the
+            # ones of prompts that are not finished yet are dropped
+            toks = self.run_step(entries, temperatures=[s.sampling_params.temperature for s, _ in entries]).tolist()
+            for (s, _), t in zip(entries, toks):
+                if s.num_computed_tokens >= s.num_prompt_tokens:
+                    self._accept(s, t)
             self.stats["decode_steps"] += 1
             finished = [s for s in running if s.status is SequenceStatus.FINISHED]
             if finished:
