@@ -5,6 +5,8 @@ the router's choice and the weighted combine are kernels of the native library (
 """
 from __future__ import annotations
 
+import warnings
+
 import torch
 import torch.nn.functional as F
 from torch import nn
@@ -110,13 +112,18 @@ class RoutedExperts(nn.Module):
         xs = x.index_select(0, order // self.top)
         counts = torch.zeros(self.n_real + self.n_identity, dtype=torch.int32, device=x.device)
         counts.index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
+        ys = None
         if self.grouped_gemm and x.dtype == torch.bfloat16 and W % 8 == 0 and self.ff % 8 == 0:
             # library grouped GEMM: segment ends stay on the device, one launch per projection, no host round trip
             # and no per-shape algorithm search (a plain GEMM with a row count it has not seen costs milliseconds)
             ends = counts[: self.n_real].cumsum(0).to(torch.int32)
-            gu = torch._grouped_mm(xs, self.gate_up.transpose(1, 2), offs=ends)
-            ys = torch._grouped_mm(gated_act(gu, self.act), self.down.transpose(1, 2), offs=ends)
-        else:
+            try:
+                gu = torch._grouped_mm(xs, self.gate_up.transpose(1, 2), offs=ends)
+                ys = torch._grouped_mm(gated_act(gu, self.act), self.down.transpose(1, 2), offs=ends)
+            except (RuntimeError, NotImplementedError) as ex:   # a shape the library's grouped kernel refuses
+                warnings.warn(f"grouped GEMM refused ({ex}); the per-expert products serve this layer from now on")
+                self.grouped_gemm = False
+        if ys is None:
             host_counts = counts[: self.n_real].tolist()
             gu = torch.empty((order.numel(), 2 * self.ff), dtype=x.dtype, device=x.device)
             ys = torch.empty((order.numel(), W), dtype=x.dtype, device=x.device)
