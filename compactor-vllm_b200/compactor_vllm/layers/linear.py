@@ -39,7 +39,7 @@ class PeerAllReduce:
         # One-shot reads (world-1) x message per rank, two-shot 2 x (world-1)/world x message plus one publishing
         # barrier; every barrier is a system-scope release / acquire pair (csrc/allreduce.cu).  Measured per call
         # inside a CUDA graph, [rows, 8192] bf16, on one 8 x B200 box (profiles/r02f_tp_allreduce_sys_n{2,4,8}.json;
-        # the relaxed-flag build of round 1 is 4-8 us faster per call, profiles/r02f_tp_allreduce_relaxed_n8.json):
+        # the earlier relaxed-flag build is 4-8 us faster per call, profiles/r02f_tp_allreduce_relaxed_n8.json):
         #   8 ranks: one-shot 12.8 / 18.8 / 26.7 / 38.5 us at 16 KB / 256 KB / 1 MB / 2 MB, two-shot 16.9 / 22.0 /
         #            26.6 / 28.3 us -> switch at 1 MB; 4 MB: 32.6 us (NCCL 55.9), 8 MB: 44.4 us (NCCL 73.2);
         #            NCCL at 16 KB .. 2 MB: 27.4 / 30.7 / 31.3 / 35.2 us

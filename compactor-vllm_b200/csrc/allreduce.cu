@@ -33,7 +33,7 @@ struct ArPeers {
 // kernel boundary orders before this kernel's fence, so the release is cumulative over it; (b) the two-shot publish
 // barrier: slices written inside this kernel; (c) the end barrier: the peer's loads of my payload are ordered before
 // its flag store by the same fence, and my acquire orders the next call's overwrite after them (write-after-read).
-// The round-1 form (volatile flags, gpu-scope fence on publish only: 1-3 us faster per call, correct on this
+// The earlier form (volatile flags, gpu-scope fence on publish only: 1-3 us faster per call, correct on this
 // hardware in every stress run but a data race under the PTX model) is kept behind -DCVLLM_AR_RELAXED_FLAGS for A/B.
 __device__ __forceinline__ void st_flag(uint32_t* p, uint32_t v) {
 #ifdef CVLLM_AR_RELAXED_FLAGS

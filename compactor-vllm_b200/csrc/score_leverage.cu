@@ -254,7 +254,7 @@ __global__ void __launch_bounds__(kLevThreads, 2) leverage_gram_kernel(const Lev
 // ---- kernel 2: symmetric eigendecomposition in fp64, one 128-thread CTA per 48x48 matrix ----
 // Why fp64: the reference's gesvda result agrees with the EXACT (fp64) eigendecomposition of the same
 // fp32 Gram to 99.3 % of the scores within 2e-2 on low-rank keys, while any norm-wise backward-stable
-// fp32 solver (cuSOLVER gesvd / gesvdj, and round 1's fp32 QL here) only reaches 60-85 %
+// fp32 solver (cuSOLVER gesvd / gesvdj, and an earlier fp32 QL here) only reaches 60-85 %
 // (profiles/r02a_leverage_selfdistance_before.json): |lam| ranges over 1e-2 .. 1e5, and an absolute
 // error of eps32 * |lam|_max ~ 1e-2 destroys the small eigenpairs that dominate x^T |G|^-1 x.
 //

@@ -1,5 +1,5 @@
 """One process driving two GPUs: every kernel with a raised dynamic-shared-memory limit must raise it per DEVICE
-(`ensure_max_dyn_smem`, csrc/common.cuh), not once per process — the round-1 library launched with the default limit
+(`ensure_max_dyn_smem`, csrc/common.cuh), not once per process — an earlier library launched with the default limit
 on the second device and failed.  Skipped on single-GPU boxes."""
 import math
 

@@ -16,11 +16,9 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def write_model(folder: Path, seed: int = 0):
-    from oracle import movolorn as O  # noqa: F401  (the dict layout)
-
+def default_config():
     W, V = 32, 50
-    cfg = {"architecture": "Movolorn", "vocab": V, "width": W, "embedding": {"scale": 0.7}, "norm": {"eps": 1e-5},
+    return {"architecture": "Movolorn", "vocab": V, "width": W, "embedding": {"scale": 0.7}, "norm": {"eps": 1e-5},
            "layers": [
                {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.2,
                                                "mask": {"size": 10}}, "mlp": {"kind": "dense", "ff": 40}},
@@ -31,6 +29,13 @@ def write_model(folder: Path, seed: int = 0):
                {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 32, "vdim": 32, "scale": 0.15},
                 "mlp": None}],
            "loop": {"start": 1, "stop": 2, "times": 2}}
+
+
+def write_model(folder: Path, seed: int = 0, cfg: dict | None = None):
+    """Writes config.json and model.safetensors of a random model of `cfg`; returns the oracle's dict of the same
+    tensors (after their bfloat16 rounding)."""
+    cfg = default_config() if cfg is None else cfg
+    W, V = cfg["width"], cfg["vocab"]
     g = torch.Generator().manual_seed(seed)
     t = {}
 
@@ -61,10 +66,12 @@ def write_model(folder: Path, seed: int = 0):
             r, f = ml["router"], ml["expert"]["ff"]
             for e in range(r["experts"]):
                 mat(p + f"mlp.e{e}.gate", f, W); mat(p + f"mlp.e{e}.up", f, W); mat(p + f"mlp.e{e}.down", W, f)
-            mat(p + "mlp.router", r["experts"] + r["identity"], W, scale=0.5)
-            t[p + "mlp.correction"] = (0.2 * torch.randn(r["experts"] + r["identity"], generator=g)).to(torch.bfloat16)
-            sf = ml["shared"]["ff"]
-            mat(p + "mlp.shared.gate", sf, W); mat(p + "mlp.shared.up", sf, W); mat(p + "mlp.shared.down", W, sf)
+            total = r["experts"] + r.get("identity", 0)
+            mat(p + "mlp.router", total, W, scale=0.5)
+            t[p + "mlp.correction"] = (0.2 * torch.randn(total, generator=g)).to(torch.bfloat16)
+            if ml.get("shared"):
+                sf = ml["shared"]["ff"]
+                mat(p + "mlp.shared.gate", sf, W); mat(p + "mlp.shared.up", sf, W); mat(p + "mlp.shared.down", W, sf)
     header, blob = {}, b""
     for name, x in t.items():
         raw = x.contiguous().view(torch.int16).numpy().tobytes()
@@ -92,13 +99,15 @@ def write_model(folder: Path, seed: int = 0):
                 entry["mlp"] = {"kind": "moe", "router": f(p + "mlp.router"), "correction": f(p + "mlp.correction"),
                                 "experts": [{k: f(p + f"mlp.e{e}.{k}") for k in ("gate", "up", "down")}
                                             for e in range(r["experts"])],
-                                "top": r["top"], "groups": r["groups"]["count"], "keep": r["groups"]["keep"],
-                                "identity": r["identity"],
-                                "shared": {k: f(p + f"mlp.shared.{k}") for k in ("gate", "up", "down")}}
+                                "top": r["top"], "groups": (r.get("groups") or {}).get("count", 1),
+                                "keep": (r.get("groups") or {}).get("keep", 1), "identity": r.get("identity", 0),
+                                "shared": ({k: f(p + f"mlp.shared.{k}") for k in ("gate", "up", "down")}
+                                           if ml.get("shared") else None)}
         layers.append(entry)
-    lp = cfg["loop"]
-    return {"embed": f("embed"), "embed_scale": 0.7, "eps": 1e-5, "final_norm": f("final.norm"), "head": f("head"),
-            "layers": layers, "loop": (lp["start"], lp["stop"], lp["times"])}
+    lp = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    return {"embed": f("embed"), "embed_scale": cfg["embedding"]["scale"], "eps": cfg["norm"]["eps"],
+            "final_norm": f("final.norm"), "head": f("head"), "layers": layers,
+            "loop": (lp["start"], lp["stop"], lp["times"])}
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 3e-5), ("bfloat16", 8e-2)])
