@@ -5,7 +5,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Workload "M" (the "@32K, 50 % keep" row): per rank ONE 32768-token sequence,
+Workload "M": per rank ONE 32768-token sequence,
 HQ=32 HKV=8 D=128 page=128 bf16, COMPACTOR compression keeping 50 % (first 16 / last 64 tokens
 protected), one transformer layer's hot path.  A *step* is one pass of that path over the
 sequence through the reference-shaped Python API:
@@ -20,9 +20,9 @@ ranks / max-over-ranks step time, i.e. sparse-attention prefill TFLOP/s WITH com
 step.  The other two numbers of the metric (decode HBM GB/s on the compacted cache, KV-compress
 Mtok/s) are measured in the same run and reported under "components".
 
-Ranks are independent sequences (weak scaling; the path has no collective, SURVEY 8e).
+Ranks are independent sequences (weak scaling; the path has no collective).
 
-`--impl reference`: the reference has no CPU implementation (SURVEY 8d); the timed CPU arm is
+`--impl reference`: the reference has no CPU implementation; the timed CPU arm is
 the oracle/ restatement of the same path on the host cores, bounded sample.
 """
 from __future__ import annotations
@@ -677,7 +677,7 @@ def run_reference_arm(args, rank: int, world: int):
         "config": cfg,
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": f"{n}-token slice of the workload (same heads, same compression), "
-                                   "oracle/ restatement: the reference has no CPU path (SURVEY 8d)"},
+                                   "oracle/ restatement: the reference has no CPU path"},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -896,7 +896,7 @@ def main():
             comps["compress_graph_error"] = repr(ex)[:200]
         comp_bytes = n_tok * (2048 + 8192 + 2048 + HKV * 4 * 4) + kept_pairs * 1024
         comps["compress_implied_gbs"] = comp_bytes / (ms_comp * 1e-3) / 1e9
-        if "compress_graph_ms" in comps:  # device time of the chain against its algorithmic bytes (SURVEY 8d)
+        if "compress_graph_ms" in comps:  # device time of the chain against its algorithmic bytes
             g_gbs = comp_bytes / (comps["compress_graph_ms"] * 1e-3) / 1e9
             comps["roofline_compress"] = {"bound": "hbm", "achieved": g_gbs, "peak": pk["hbm"], "unit": "GB/s",
                                           "frac": g_gbs / pk["hbm"], "bytes": comp_bytes,

@@ -1,7 +1,7 @@
 """compactor_vllm — B200-native attention + KV-compression hot path.
 
 Import paths mirror vnchari/compactor-vllm (src/compactor_vllm/__init__.py:7-17).  `LLM` is the
-engine shell of SURVEY 8(f)-3 (core/llm_engine.py): single rank, synthetic weights, CUDA-graph
+engine shell (core/llm_engine.py): single rank, synthetic weights, CUDA-graph
 decode — it exists to drive the hot path through the reference's top-level call; tokenizer
 download, HF checkpoint loading and multi-process tensor parallelism are outside this build.
 """

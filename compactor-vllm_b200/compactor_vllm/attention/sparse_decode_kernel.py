@@ -3,7 +3,7 @@
 `head_sparse_decode_attention` keeps the reference signature; `key_split` is
 accepted and ignored except for validation — the sm_100a kernel balances work
 over 128-token units of every (batch, kv-head) itself and merges in-kernel, so
-the result does not depend on it (SURVEY §9.13).  `num_splits_heuristic` is kept
+the result does not depend on it.  `num_splits_heuristic` is kept
 because the reference's model runner imports it (core/model_runner.py:7,503).
 """
 from __future__ import annotations

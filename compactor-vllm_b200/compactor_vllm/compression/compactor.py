@@ -45,7 +45,7 @@ class CompactorCompression(BaseCompressionMethod):
     def post_rope_scoring(q, k, v, pre_rope_scores, context) -> Optional[torch.Tensor]:
         cc = context.compression_context
         # The reference launches this on the main stream while pre_rope_scores is still being
-        # produced on STORE_STREAM without a wait (compactor.py:44-59, SURVEY 7.3-7).  Here the
+        # produced on STORE_STREAM without a wait (compactor.py:44-59).  Here the
         # whole scoring chain stays on STORE_STREAM: it is ordered after the leverage kernels by
         # the stream itself, its only consumer (extract_and_store_top_kv in Attention.forward)
         # runs on the same stream, and the attention kernel on the main stream starts without

@@ -1,4 +1,4 @@
-"""`LLM` — the engine shell's public entry (SURVEY 8(f)-3; reference: core/llm_engine.py:34-294).
+"""`LLM` — the engine shell's public entry (reference: core/llm_engine.py:34-294).
 
 Same call shape as the reference's `LLMEngine.generate`: prompts (token-id lists, or strings when a
 tokenizer is available locally), `SamplingParams`, `BatchCompressionParams`, optional per-sequence

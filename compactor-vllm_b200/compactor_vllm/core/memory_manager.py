@@ -1,4 +1,4 @@
-"""KV cache manager (SURVEY row a14): how many pages fit, which slot a sequence lives in, and the
+"""KV cache manager: how many pages fit, which slot a sequence lives in, and the
 wiring of the per-layer cache views into the attention modules.
 
 The reference's class (core/memory_manager.py:13-182) mixes three things in its methods: reading the CUDA
@@ -170,7 +170,7 @@ class KVCacheManager:
     # ---- the cache ------------------------------------------------------------------------------
     def init_cache(self, model: nn.Module, num_pages: Optional[int] = None, device_allocator: bool = False):
         """Size the cache (unless `num_pages` is given), allocate it and hand every attention layer its views.
-        device_allocator=True: the GPU-resident page allocator (same surface, same page ids; SURVEY 8(f)-2)."""
+        device_allocator=True: the GPU-resident page allocator (same surface, same page ids)."""
         cache_type = DevicePagedKVCache if device_allocator else PagedKVCache
         if hasattr(model, "cache_specs"):
             return self._init_cache_from_specs(model.cache_specs(), num_pages, cache_type)

@@ -1,4 +1,4 @@
-"""Single-rank model runner of the engine shell (SURVEY 8(f)-3; reference: core/model_runner.py:32-555).
+"""Single-rank model runner of the engine shell (reference: core/model_runner.py:32-555).
 
 What it keeps of the reference: prefill batches packed by a token budget (core/scheduler.py:65-108),
 per-sequence retain budgets and PHI (utils/arguments.py:81-121), the global `Context` set before each
@@ -37,8 +37,8 @@ def _pad_batch(n: int) -> int:
 
 
 def _check_shape_envelope(hf, config: LLMConfig) -> None:
-    """Fail at construction, with the reason, for geometries the sm_100a kernels do not serve (INTEGRATION.md
-    section 3: the per-call answer would be CVLLM_E_UNSUPPORTED in the middle of the first prefill)."""
+    """Fail at construction, with the reason, for geometries the sm_100a kernels do not serve (the per-call
+    answer would be CVLLM_E_UNSUPPORTED in the middle of the first prefill)."""
     head_dim = getattr(hf, "head_dim", None) or hf.hidden_size // hf.num_attention_heads
     group = hf.num_attention_heads // hf.num_key_value_heads
     problems = []
@@ -63,7 +63,7 @@ class KVCacheExhausted(RuntimeError):
 class ModelRunner:
     def __init__(self, config: LLMConfig, *, num_pages: Optional[int] = None, seed: int = 0,
                  device_allocator: bool = True, max_batched_tokens: Optional[int] = None):
-        assert config.tensor_parallel_size == 1, "the engine shell is single-rank (TP is SURVEY 8(f)-4)"
+        assert config.tensor_parallel_size == 1, "the engine shell is single-rank (tensor parallelism: layers/linear.py)"
         assert torch.cuda.is_available(), "no CPU fallback"
         self.config = config
         hf = config.hf_config

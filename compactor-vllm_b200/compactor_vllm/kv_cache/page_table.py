@@ -108,7 +108,7 @@ class PagedKVCache(torch.nn.Module):
             return KVAllocationStatus.SUCCESS
         # clamp at 0: heads with a spare page would otherwise get a negative count (the
         # reference does not clamp, :164-166; harmless there because the engine only ever
-        # reserves for fresh slots where all heads are equal) -- deliberate fix, see DESIGN.md
+        # reserves for fresh slots where all heads are equal) -- a deliberate fix
         add_pages = cdiv(need - cap, self.page_size).clamp_min(0)
         new_total = pages + add_pages
         if bool((new_total > self.max_pages_per_head).any()):
@@ -184,7 +184,7 @@ class PagedKVCache(torch.nn.Module):
 
 
 class DevicePagedKVCache(PagedKVCache):
-    """PagedKVCache whose page allocator lives on the GPU (SURVEY 8(f)-2, csrc/page_alloc.cu).
+    """PagedKVCache whose page allocator lives on the GPU (csrc/page_alloc.cu).
 
     Same constructor, methods, return values and — bit for bit — the same page ids as the host
     allocator above (and the reference's heaps): the free set of a layer is a bitmap, "pop the n

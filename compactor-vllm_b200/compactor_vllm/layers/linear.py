@@ -1,4 +1,4 @@
-"""Row-parallel linear + the tensor-parallel all-reduce behind it (SURVEY 8(f)-4; reference:
+"""Row-parallel linear + the tensor-parallel all-reduce behind it (reference:
 layers/linear.py:133-153 `RowParallelLinear`: `F.linear` then `dist.all_reduce(y)`).
 
 `PeerAllReduce` is the B200 route for decode-size messages: every rank keeps one cudaIpc-shared staging

@@ -5,7 +5,7 @@
 `[max_position, 1, rotary_dim]` buffer (cos | sin, llama3 frequency scaling :31-60).
 `forward(positions, query, key)` returns the rotated `(query, key)`.
 
-`fused_qk_norm_rope` is the B200 extension (SURVEY 8(f)-1): Qwen3's per-head q_norm / k_norm, the
+`fused_qk_norm_rope` is the B200 extension: Qwen3's per-head q_norm / k_norm, the
 Compactor sketch `X = K_pre . PHI` and the rotation in ONE pass over q and k — the reference runs
 four kernels, each reading and writing q / k in full (models/qwen3.py:90-97,
 compression/compactor.py:153-158).  There is no CPU / eager fallback.

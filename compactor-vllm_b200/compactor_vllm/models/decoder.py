@@ -1,12 +1,12 @@
 """Decoder-only transformer around the hot path (reference: models/llama3.py:20-281, models/qwen3.py:21-272).
 
-Engine shell of SURVEY 8(f)-3: the model exists so that `LLM.generate` drives the attention +
+Engine shell: the model exists so that `LLM.generate` drives the attention +
 KV-compression path the way the reference's models do.  The attention block is the B200 one — fused
 q/k norm + sketch + RoPE (`cvllm_rope_qk`), scoring on the store stream, `Attention.forward` — and
 the norms are `cvllm_rmsnorm`; the projections / MLP / embedding are plain library GEMMs
 (`torch.nn.functional.linear` = cuBLAS), which is what they are in the reference too
 (layers/linear.py).  Single rank (tensor_parallel_size == 1): the TP all-reduce after o_proj is
-SURVEY 8(f)-4.  Weights: random init from a seed (`init_synthetic_weights`) or a state dict with the
+layers/linear.py.  Weights: random init from a seed (`init_synthetic_weights`) or a state dict with the
 reference's packed names (`qkv_proj`, `gate_up_proj`) via `load_state_dict`; there are no checkpoint
 files on the GPU box.
 """

@@ -1,5 +1,5 @@
 // One-shot all-reduce over NVLink peer memory for the tensor-parallel o_proj / down_proj outputs of a
-// decode step (SURVEY 8(f)-4; reference: layers/linear.py:149-153 `dist.all_reduce` after the row-parallel
+// decode step (reference: layers/linear.py:149-153 `dist.all_reduce` after the row-parallel
 // GEMM).  A decode-size message ([B, hidden] bf16: 16 KB .. 1 MB) is latency-bound: NCCL's ring / tree
 // costs several hops and a proxy wake-up; here every rank reads all peers' buffers directly through
 // NVSwitch (900 GB/s per direction, any-to-any) and sums them in rank order in fp32, so every rank

@@ -23,7 +23,7 @@
 //   * partial (m, l, O) of a range that does not cover its whole head goes to
 //     a scratch slot; the CTA that completes a head merges (atomic ticket),
 //     every warp folding a strided subset of the slots with independent loads
-// HBM-bound: 4*D bytes per cached (token, head) — see DESIGN.md.
+// HBM-bound: 4*D bytes per cached (token, head).
 #include <stdlib.h>
 
 #include "common.cuh"

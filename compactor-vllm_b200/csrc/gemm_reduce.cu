@@ -1,4 +1,4 @@
-// Row-parallel linear FUSED with its tensor-parallel all-reduce (SURVEY 8(f)-4; reference: layers/linear.py:133-153
+// Row-parallel linear FUSED with its tensor-parallel all-reduce (reference: layers/linear.py:133-153
 // `RowParallelLinear.forward` = `F.linear(x, W)` then `dist.all_reduce(y)`, the o_proj of models/llama3.py:111).
 //
 //   y[M, N] = sum over ranks r of  bf16( x_r[M, K_r] . W_r[N, K_r]^T )        (fp32 sum in rank order, rounded once)

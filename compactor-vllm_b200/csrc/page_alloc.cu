@@ -1,4 +1,4 @@
-// Device-side page allocator (SURVEY 8(f)-2): the reference keeps per-layer min-heaps of free physical
+// Device-side page allocator: the reference keeps per-layer min-heaps of free physical
 // pages on the HOST (kv_cache/page_table.py:111-115) and pays two device->host syncs (`.all()`,
 // `.tolist()`), a Python heap loop and a host->device copy per reservation (:144-198), three syncs per
 // reclaim (:200-267).  Here the free set of a layer is a bitmap in HBM and "pop the n smallest pages"

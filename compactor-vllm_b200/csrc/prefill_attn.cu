@@ -18,7 +18,7 @@
 //                  as bf16 over the S columns it came from; epilogue O / l.
 //
 // TMEM: S0 [0,128) S1 [128,256) O [256,384)  (fp32 columns, 128 lanes).
-// Tensor-pipe bound: 4*D flops per (query row, key) pair — see DESIGN.md.
+// Tensor-pipe bound: 4*D flops per (query row, key) pair.
 #include <stdlib.h>
 
 #include "common.cuh"

@@ -12,7 +12,7 @@
 //   u   = round16(Xc . round16(V |lam|^-1/2));  score = round16(sum_j round16(u_j^2))
 //
 // The reference keeps X, Xc, G, V S^-1/2, U and the row sums in K's 16-bit
-// dtype (SURVEY 9.7); rounding G entrywise perturbs it by far more than the
+// dtype; rounding G entrywise perturbs it by far more than the
 // 5e-3 regulariser (it can even go indefinite: the SVD then yields |lam|), so
 // those rounding points are part of the reference's scores and are reproduced
 // here — an exact fp32 x^T G^-1 x only overlaps ~80 % with the reference's

@@ -1,8 +1,8 @@
 // Fused top-k eviction + paged-cache compaction, multi-CTA.
 //
 // Reference: compression/common.py:126-168 (scores -> torch.topk full sort -> K4 atomic-slot store
-// -> K5 serial pad walk, kv_cache/store_kv_cache.py:9-248).  The closed form (SURVEY
-// 7.3-4): after the per-sequence global top-`retain`, head h holds c_h pairs; it is padded to
+// -> K5 serial pad walk, kv_cache/store_kv_cache.py:9-248).  The closed form:
+// after the per-sequence global top-`retain`, head h holds c_h pairs; it is padded to
 // n_h = min(c_h + pad, len) and its kept set is exactly the top-n_h tokens OF THAT HEAD.  So:
 //
 //   phase 1  4 radix passes (8 bits each) over all len*H keys of a sequence  -> threshold T, ties

@@ -113,7 +113,7 @@ int cvllm_scatter_pages(const int32_t* add_pages, const int32_t* new_phys,
                         int L, int H, int max_pages_per_head, cvllm_stream_t stream);
 
 /* ------------------------------------------------------------------------
- * Device-side page allocator (SURVEY 8(f)-2) — PagedKVCache.reserve_tokens /
+ * Device-side page allocator — PagedKVCache.reserve_tokens /
  * reclaim_pages / free_batch, kv_cache/page_table.py:144-291, without the
  * host heaps: the free set of a layer is a bitmap (bit set = page free), "pop
  * the n smallest ids" is a popcount scan.  Same page ids as the reference's
@@ -148,7 +148,7 @@ int cvllm_pages_release(uint32_t* free_bits, int32_t* free_count, const int32_t*
                         int reserved_batch, cvllm_stream_t stream);
 
 /* ------------------------------------------------------------------------
- * The step after the path (SURVEY 8(f)-4): the tensor-parallel all-reduce
+ * The step after the path: the tensor-parallel all-reduce
  * behind o_proj / down_proj — layers/linear.py:149-153 `dist.all_reduce(y)`.
  * One-shot all-reduce over NVLink peer memory for decode-size messages;
  * every rank reads all peers' buffers and sums in rank order (fp32), so all
@@ -325,7 +325,7 @@ int cvllm_leverage_scores_from_sketch(const void* sketch_rows, const int32_t* ch
                                       cvllm_stream_t stream);
 
 /* ------------------------------------------------------------------------
- * The step in front of the path (SURVEY 8(f)-1)
+ * The step in front of the path
  * --------------------------------------------------------------------- */
 
 /* RotaryEmbedding.forward — layers/rotary_embedding.py:69-80 (neox

@@ -1,4 +1,4 @@
-"""Oracle for the step in front of the hot path (SURVEY 8(f)-1): per-head RMSNorm, the Compactor
+"""Oracle for the step in front of the hot path: per-head RMSNorm, the Compactor
 sketch of the pre-RoPE keys, and the rotary embedding.  TEST INFRASTRUCTURE ONLY (see __init__).
 
 Plain torch on CPU in the reference's eager arithmetic; pinned by tests/golden/rope_*.npz and

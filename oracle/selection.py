@@ -11,7 +11,7 @@ def sort_keys(scores: np.ndarray) -> np.ndarray:
     """Order-preserving uint32 key of fp32 scores; NaN ranks above +inf.
 
     torch.topk treats NaN as the largest value (compression/common.py:240-242
-    relies on it for the 0/0 z-scores, SURVEY 9.6).  -0.0 orders just below +0.0.
+    relies on it for the 0/0 z-scores).  -0.0 orders just below +0.0.
     """
     bits = np.ascontiguousarray(scores, dtype=np.float32).view(np.uint32)
     key = np.where(bits & 0x80000000, ~bits, bits | np.uint32(0x80000000)).astype(np.uint32)

@@ -1,4 +1,4 @@
-"""Page allocator parity (SURVEY 8(a)-a13, 8(f)-2): the host allocator (`PagedKVCache`) and the
+"""Page allocator parity: the host allocator (`PagedKVCache`) and the
 device-side allocator (`DevicePagedKVCache`, csrc/page_alloc.cu) against the trace of the REFERENCE's
 PagedKVCache (tests/golden/allocator_trace.npz, oracle/gen_golden.py) — return values, page tables,
 page counts and the free set after every operation, exact — plus randomised host-vs-device agreement,

@@ -1,4 +1,4 @@
-"""GPU parity of the step after the hot path (SURVEY 8(f)-4): the one-shot peer-memory all-reduce behind
+"""GPU parity of the step after the hot path: the one-shot peer-memory all-reduce behind
 `RowParallelLinear` (reference layers/linear.py:133-153).  On one GPU the kernel runs with world == 1 (own
 buffer only: barrier words, epochs, staging and graph replay are all exercised); with >= 2 GPUs visible the
 2-rank check in tools/tp_allreduce_check.py is launched as one process per GPU.

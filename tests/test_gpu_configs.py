@@ -200,7 +200,7 @@ def test_config2_llama8b_16k_compactor_prefill_then_decode():
     q, k, v, k_pre = _qkv(N, HQ, HKV, 2)
     eng = Engine(HQ, HKV, [N], extra_tokens=3 * PS)
     out, scores = eng.prefill(q, k, v, k_pre, CompressionMethod.COMPACTOR, 0.5, first, last)
-    assert eng.retain == [65216]  # SURVEY 8(d)
+    assert eng.retain == [65216]
     rows = [0, 63, 64, 1000, 8191, 8192, 16383]
     assert rel_err(out[rows], _ref_rows(q, k, v, rows, HKV, 1.0 / math.sqrt(D))) < 2e-2
     sc = scores.float().cpu()
@@ -223,7 +223,7 @@ def test_config3_qwen8b_snapkv_25pct_40k_batch16_decode():
         eng.cu = torch.tensor([0, N], dtype=torch.int32, device=DEV)
         slots, eng.slots = eng.slots, [eng.slots[b]]
         # the engine's default protected counts (16 / 64) size the budget (utils/arguments.py:109-121 ->
-        # SURVEY's 81760 pairs); SnapKV itself force-keeps only its 32-key observation window (snapkv.py:27-35)
+        # 81760 pairs); SnapKV itself force-keeps only its 32-key observation window (snapkv.py:27-35)
         out, scores = eng.prefill(q, k, v, None, CompressionMethod.SNAPKV, 0.25, 16, 64)
         assert eng.retain == [81760]
         if b in (0, B - 1):  # full eviction check on two sequences (a few seconds of oracle each)

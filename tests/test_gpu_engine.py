@@ -1,4 +1,4 @@
-"""Engine shell (SURVEY 8(f)-3): `LLM.generate` drives the hot path end to end — prefill with scoring and
+"""Engine shell: `LLM.generate` drives the hot path end to end — prefill with scoring and
 compaction on the store stream, page reclaim, CUDA-graph decode — on a small synthetic-weight model.
 
 Parity: without compression the engine's greedy tokens are checked against a plain fp32 torch

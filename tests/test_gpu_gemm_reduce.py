@@ -1,4 +1,4 @@
-"""GPU parity of the fused row-parallel linear + all-reduce (SURVEY 8(f)-4; reference layers/linear.py:133-153:
+"""GPU parity of the fused row-parallel linear + all-reduce (reference layers/linear.py:133-153:
 `F.linear(x, W_shard)` then `dist.all_reduce(y)`), csrc/gemm_reduce.cu through the C ABI `cvllm_gemm_allreduce`.
 
 On ONE GPU the whole protocol runs with several VIRTUAL ranks: `world` buffers in this process, `world` kernels on

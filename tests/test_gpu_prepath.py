@@ -1,4 +1,4 @@
-"""GPU parity of the step in front of the hot path (SURVEY 8(f)-1): `cvllm_rope_qk` (RoPE, optional
+"""GPU parity of the step in front of the hot path: `cvllm_rope_qk` (RoPE, optional
 per-head RMSNorm, optional Compactor sketch) and `cvllm_rmsnorm`, through the reference-shaped layers.
 
 Bars: the rotation is bit-exact against the oracle and the reference's golden vectors (same fp32

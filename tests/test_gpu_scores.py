@@ -1,7 +1,7 @@
 """Key scorers (Compactor leverage + chunk attention mass, SnapKV) vs the CPU oracle and the
 reference-generated goldens.
 
-Tolerance (SURVEY 8c): finite entries |d| <= 2e-2 * max(1, |s|), +-inf pattern exact.  The
+Tolerance: finite entries |d| <= 2e-2 * max(1, |s|), +-inf pattern exact.  The
 leverage chain is ill-conditioned by construction in the reference (every intermediate lives in
 K's 16-bit dtype, and the z-score divides by a chunk's std), so next to the element tolerance it
 is judged the way it is used: overlap of the top-50 % kept set."""
@@ -214,7 +214,7 @@ def test_leverage_golden(name):
     for L in chunk_lens:
         full[off:off + L] = L >= 48
         off += L
-    # z-scores live in 16-bit storage on both sides (SURVEY 9.7): the bound is relative to the
+    # z-scores live in 16-bit storage on both sides: the bound is relative to the
     # score magnitude (2 bf16 ulps at |z| in [4, 8) is already 0.06)
     ref_n = g["norm"].float()[full].flatten()
     dn = (norm.float().cpu()[full].flatten() - ref_n).abs() / ref_n.abs().clamp_min(1.0)
@@ -336,7 +336,7 @@ def test_leverage_matches_reference_arithmetic_on_device(dtype, lens, chunk):
 
 
 def test_leverage_one_token_chunk_is_nan():
-    """a 1-token tail chunk z-scores to 0/0 = NaN, which the ranking keeps first."""
+    """A 1-token tail chunk z-scores to 0/0 = NaN, which the ranking keeps first."""
     lens, H = [513], 8
     keys = _structured_keys(sum(lens), H, 128, torch.bfloat16, seed=5)
     phi = make_phi(128, 48, torch.bfloat16, "cpu")

@@ -95,7 +95,7 @@ def test_slot_map_reuses_and_releases():
 
 
 def test_shape_envelope_is_checked_at_construction():
-    """INTEGRATION.md section 3: D != 128 etc. are refused by name before any kernel is launched."""
+    """D != 128 etc. are refused by name before any kernel is launched."""
     from types import SimpleNamespace as NS
 
     from compactor_vllm.core.model_runner import _check_shape_envelope

@@ -174,7 +174,7 @@ def test_leverage_matches_reference(name):
     assert len(mine & ref) / k >= 0.99
 
 
-# ---- the step in front of the path: RoPE / RMSNorm (SURVEY 8(f)-1), reference modules run eager ----
+# ---- the step in front of the path: RoPE / RMSNorm, reference modules run eager ----
 @pytest.mark.parametrize("name", ["rope_bf16_llama3", "rope_f16_plain"])
 def test_rope_oracle_and_cache_match_reference(name):
     from oracle import prepath as op

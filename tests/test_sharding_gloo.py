@@ -1,4 +1,4 @@
-"""N > 1 host logic on CPU: two ranks over gloo (SURVEY 8e: the path shards by KV head with no
+"""N > 1 host logic on CPU: two ranks over gloo (the path shards by KV head with no
 exchange; the only collectives are the harness's barrier / max / sum)."""
 import os
 import socket

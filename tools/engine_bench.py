@@ -1,4 +1,4 @@
-"""End-to-end numbers through `LLM` (SURVEY 8(f)-3) at BASELINE.json's model shapes with synthetic weights:
+"""End-to-end numbers through `LLM` at BASELINE.json's model shapes with synthetic weights:
 
     python tools/engine_bench.py --model llama-3.1-8b --prompt 16384 --ratio 0.5 --method COMPACTOR --new 256
     python tools/engine_bench.py --model qwen3-8b --prompt 40960 --ratio 0.25 --method SNAPKV --batch 16 --new 64

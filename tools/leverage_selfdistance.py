@@ -1,4 +1,4 @@
-"""How far is the reference's leverage scorer from ITSELF, and how far is this repo from it?  (task 1)
+"""How far is the reference's leverage scorer from ITSELF, and how far is this repo from it? 
 
     python tools/leverage_selfdistance.py            # both sides as subprocesses -> gpurun_out/r02_leverage_selfdistance.json
 

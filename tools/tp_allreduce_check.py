@@ -1,4 +1,4 @@
-"""Multi-GPU check + timing of the one-shot peer all-reduce (SURVEY 8(f)-4).  One process per GPU:
+"""Multi-GPU check + timing of the one-shot peer all-reduce.  One process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
         tools/tp_allreduce_check.py
