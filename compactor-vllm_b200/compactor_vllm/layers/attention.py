@@ -148,12 +148,16 @@ class BiasedChunkAttention(nn.Module):
         return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.v_head_dim
 
     def decode_splits(self, batch: int, max_keys: int) -> int:
-        """Parts a sequence's keys are cut into for a decode step: as many as keep all CTAs in ONE wave of two per SM
-        (148 SMs), at least 128 keys per part.  `max_keys` bounds the keys a query can see (the chunk bounds it
-        further)."""
+        """Parts a sequence's keys are cut into for a decode step.  Small steps: as many as fill ONE wave of two CTAs
+        per SM (148 SMs) with at least 128 keys per part.  Large steps (many sequences or long contexts) run faster
+        with several waves of shorter CTAs, as long as a part keeps 256 keys: measured at 32 / 8 heads of 128, 8 x 16384
+        keys 1.72 -> 2.18 TB/s (4 -> 32 parts), 32 x 4096 keys 1.74 -> 2.27 TB/s (1 -> 8 parts).  `max_keys` bounds the
+        keys a query can see (the chunk bounds it further)."""
         keys = min(max_keys, self.chunk) if self.chunk else max_keys
-        ctas = batch * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 4)
-        return int(max(1, min(296 // max(ctas, 1), keys // 128, 64)))
+        ctas = max(batch * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 4), 1)
+        one_wave = min(296 // ctas, keys // 128)
+        several = min(2048 // ctas, keys // 256)
+        return int(max(1, min(max(one_wave, several), 64)))
 
     def forward(self, qkv: torch.Tensor) -> torch.Tensor:
         from compactor_vllm import _native as N

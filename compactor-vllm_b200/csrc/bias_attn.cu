@@ -581,6 +581,7 @@ constexpr int kDecTile = 4;   // query heads per CTA
 // scores are kept in log2 units (log2(e) folded into the query scale and the slopes), so every exponential of the
 // split and merge kernels is one ex2.approx
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kDecSlack = 8.f;   // how far a logit may pass the running reference point before it moves
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float* v);
@@ -800,7 +801,10 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
       v += __shfl_xor_sync(gmask, v, 2);
       v += __shfl_xor_sync(gmask, v, 1);
       v -= slope[r] * dist;
-      if (v > m[r]) {   // the same for the 8 lanes of the group
+      // The reference point m moves only when a logit passes it by more than kDecSlack (log2 units): weights stay
+      // below 2^kDecSlack, far inside fp32, and the result is the same sum.  With a distance bias the logits of
+      // later keys keep rising, so an exact running maximum would rescale the accumulators at almost every key.
+      if (v > m[r] + kDecSlack) {   // the same for the 8 lanes of the group
         const float corr = ex2(m[r] - v);
         l[r] *= corr;
 #pragma unroll
