@@ -150,13 +150,14 @@ class BiasedChunkAttention(nn.Module):
     def decode_splits(self, batch: int, max_keys: int) -> int:
         """Parts a sequence's keys are cut into for a decode step.  Small steps: as many as fill ONE wave of two CTAs
         per SM (148 SMs) with at least 128 keys per part.  Large steps (many sequences or long contexts) run faster
-        with several waves of shorter CTAs, as long as a part keeps 256 keys: measured at 32 / 8 heads of 128, 8 x 16384
-        keys 1.72 -> 2.18 TB/s (4 -> 32 parts), 32 x 4096 keys 1.74 -> 2.27 TB/s (1 -> 8 parts).  `max_keys` bounds the
-        keys a query can see (the chunk bounds it further)."""
+        with several waves of shorter CTAs while a part keeps 1024 keys: measured at 32 / 8 heads of 128, 8 x 16384
+        keys 1.75 -> 2.05 TB/s (4 -> 16 parts), 32 x 4096 keys 1.74 -> 2.15 TB/s (1 -> 4 parts); thinner parts lose
+        again to the merge pass when the bound `max_keys` is well above the keys really there (graph replays).
+        `max_keys` bounds the keys a query can see (the chunk bounds it further)."""
         keys = min(max_keys, self.chunk) if self.chunk else max_keys
         ctas = max(batch * self.num_kv_heads * -(-(self.num_heads // self.num_kv_heads) // 4), 1)
         one_wave = min(296 // ctas, keys // 128)
-        several = min(2048 // ctas, keys // 256)
+        several = min(2048 // ctas, keys // 1024)
         return int(max(1, min(max(one_wave, several), 64)))
 
     def forward(self, qkv: torch.Tensor) -> torch.Tensor:
