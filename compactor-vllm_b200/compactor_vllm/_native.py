@@ -77,17 +77,26 @@ _SIGNATURES = {
     "cvllm_snapkv_scores": (_i, [_p, _p, _i64, _i64, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f, _i,
                                  _i, _p, _i, _p, _sz, _p]),
     "cvllm_selftest_umma": (_i, [_p, _p, _p, _i, _u32, _u32, _i, _p]),
-    "cvllm_sandwich_norm": (_i, [_p, _i64, _i, _p, _p, _i64, _p, _p, _i64, _i, _i, _i, _f, _p]),
-    "cvllm_gated_act": (_i, [_p, _i64, _p, _i64, _i64, _i, _i, _i, _p]),
-    "cvllm_moe_route": (_i, [_p, _i64, _p, _i, _i, _i, _i, _i, _p, _p, _p]),
-    "cvllm_moe_combine": (_i, [_p, _p, _p, _i, _p, _i, _p, _p, _p, _i64, _i, _i, _p]),
-    "cvllm_expert_gemv": (_i, [_p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _p]),
+    "cvllm_sandwich_norm": (_i, [_p, _i64, _i, _p, _p, _i64, _p, _p, _i64, _i, _i, _i, _f, _f, _i, _p]),
+    "cvllm_gated_act": (_i, [_p, _i64, _p, _i64, _i64, _i, _i, _f, _i, _p]),
+    "cvllm_moe_route": (_i, [_p, _i64, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p]),
+    "cvllm_moe_combine": (_i, [_p, _p, _p, _i, _p, _i, _p, _p, _p, _i64, _p, _i64, _i, _i, _p]),
+    "cvllm_expert_gemv": (_i, [_p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _f, _i, _p]),
+    "cvllm_latent_norm_store": (_i, [_p, _i64, _i, _i, _i, _i, _i, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i, _p,
+                                     _i, _i, _i, _p]),
+    "cvllm_latent_q_rope": (_i, [_p, _i64, _i, _i, _i, _p, _p, _p, _i64, _i, _i, _i, _i, _p]),
+    "cvllm_sigmoid_gate": (_i, [_p, _i64, _p, _i64, _p, _i64, _i64, _i, _i, _p]),
+    "cvllm_causal_conv": (_i, [_p, _i64, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i64, _i, _p]),
+    "cvllm_conv_state_update": (_i, [_p, _i64, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
+    "cvllm_ssm_scan": (_i, [_p, _i64, _p, _i64, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _i64, _i, _i, _i, _i,
+                            _i, _i, _p]),
+    "cvllm_gated_group_norm": (_i, [_p, _i64, _p, _i64, _p, _f, _p, _i64, _i64, _i, _i, _i, _p]),
     "cvllm_qknorm_store": (_i, [_p, _i64, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
                                 _i, _i, _i, _i, _i, _i, _i, _p]),
     "cvllm_bias_attn_varlen": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _p, _i, _i, _f, _p,
-                                    _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i, _p]),
+                                    _i, _i, _i, _i, _i, _i, _i, _i64, _i, _i64, _i, _p]),
     "cvllm_bias_attn_decode": (_i, [_p, _p, _p, _p, _i64, _i64, _i, _p, _p, _p, _i, _i, _f, _p,
-                                    _i, _i, _i, _i, _i, _i, _i, _p, _sz, _i, _p]),
+                                    _i, _i, _i, _i, _i, _i, _i, _p, _sz, _i64, _i, _p]),
 }
 
 _lib = None

@@ -197,7 +197,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
         N.check(lib.cvllm_bias_attn_varlen(N.ptr(q), N.ptr(attn.k_cache), N.ptr(attn.v_cache), *table,
                                            N.ptr(c.cu_seqlens_q), N.ptr(c.seq_start), N.ptr(c.batch_mapping),
                                            N.ptr(attn.slopes), attn.chunk, 1, attn.scale, N.ptr(out), 1, L, H, G, D, D,
-                                           L, attn.k_cache.shape[0], pt.shape[-1], code, N.stream(dev)), "varlen")
+                                           L, attn.k_cache.shape[0], pt.shape[-1], 0, code, N.stream(dev)), "varlen")
 
     prefill_ctx(0)
     add("qknorm_store", timed(store), nbytes=2 * L * ((H + 2 * G) * D + (H + 2 * G) * D),
@@ -219,7 +219,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
         ws = N.workspace(dev, 4 * B * H * splits * (2 + D), "bias_attn_decode")
         N.check(lib.cvllm_bias_attn_decode(N.ptr(qd), N.ptr(attn.k_cache), N.ptr(attn.v_cache), *table, N.ptr(pos),
                                            N.ptr(bm), N.ptr(attn.slopes), chunk, 1, attn.scale, N.ptr(od), B, H, G, D, D,
-                                           0, splits, N.ptr(ws), ws.numel(), code, N.stream(dev)), "decode")
+                                           0, splits, N.ptr(ws), ws.numel(), 0, code, N.stream(dev)), "decode")
 
     add("bias_attn_decode (no chunk, 8 x 4096)", timed(lambda: decode(0)), nbytes=2 * 2 * B * G * L * D,
         like="decode_attn_kernel")
@@ -234,7 +234,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
     a = torch.empty(B * top, Fe, dtype=bf, device=dev)
     add("expert_gemv (gate | up, 16 pairs)",
         timed(lambda: N.check(lib.cvllm_expert_gemv(N.ptr(xs), top, N.ptr(wgu), N.ptr(idx), Ee, N.ptr(a), B * top, Fe, W,
-                                                    0, code, N.stream(dev)), "gemv")),
+                                                    0, 0.0, code, N.stream(dev)), "gemv")),
         nbytes=2 * B * top * 2 * Fe * W, like="cuBLAS GEMV-shaped GEMM of the dense models")
     return rows
 

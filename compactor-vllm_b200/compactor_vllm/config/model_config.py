@@ -132,7 +132,157 @@ class MovolornConfig:
         return max(l.mixer.dim for l in self.layers)
 
 
-ARCHITECTURES = {"Movolorn": MovolornConfig}
+@dataclass
+class LatentAttentionConfig:
+    """Attention whose queries and keys/values pass through low-rank latents (layers/latent_attention.py): `heads`
+    heads with `dim` unrotated + `rot_dim` rotated query/key numbers and `vdim` values each; the kv latent has
+    `kv_rank` numbers, the query latent `q_rank`; `kv_from` names the layer whose cached latent this layer reads
+    instead of making its own."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    scale: float
+    rot_base: float
+    kv_from: Optional[int] = None
+
+    @classmethod
+    def from_json(cls, m: dict) -> "LatentAttentionConfig":
+        rot = m.get("rot") or {}
+        rot_dim = int(m.get("rot_dim", rot.get("dims", 0)))
+        if int(rot.get("dims", rot_dim)) != rot_dim:
+            raise ValueError("latent attention rotates its whole rotated part: rot.dims must equal rot_dim")
+        if rot_dim % 2:
+            raise ValueError(f"rot_dim {rot_dim} is odd")
+        dim = int(m["dim"])
+        kv_from = m.get("kv_from")
+        return cls(heads=int(m["heads"]), dim=dim, rot_dim=rot_dim, vdim=int(m.get("vdim", dim)),
+                   kv_rank=int(m["kv_rank"]), q_rank=int(m["q_rank"]),
+                   scale=float(m.get("scale", (dim + rot_dim) ** -0.5)), rot_base=float(rot.get("base", 10000.0)),
+                   kv_from=None if kv_from is None else int(kv_from))
+
+
+@dataclass
+class StateSpaceConfig:
+    """Scalar-decay state-space mixer (layers/ssm.py): `heads` heads of `vdim` channels with `state` state channels,
+    B and C shared by the heads of each of `groups` groups, a causal convolution of `conv` taps in front and an RMS
+    norm in `norm_groups` equal parts behind."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+
+    @classmethod
+    def from_json(cls, m: dict) -> "StateSpaceConfig":
+        c = cls(heads=int(m["heads"]), vdim=int(m["vdim"]), state=int(m["state"]), groups=int(m.get("groups", 1)),
+                conv=int(m.get("conv", 4)), norm_groups=int(m.get("norm_groups", 1)))
+        if c.heads % c.groups or (c.heads * c.vdim) % c.norm_groups:
+            raise ValueError(f"state-space mixer: {c.heads} heads do not split into {c.groups} groups / "
+                             f"{c.norm_groups} norm parts")
+        return c
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
+
+
+@dataclass
+class ClampedMoEConfig:
+    """Mixture of clamped gated experts (layers/moe.py, ACT_CLAMPED_GLU + ROUTE_TOP_LOGITS): `experts` experts of
+    size `ff`, `top` per token chosen by the largest router logits (with a bias), weights = softmax over the chosen;
+    a shared expert of size `shared_ff` (0 = none) scaled by the sigmoid of one logit per token."""
+    ff: int
+    limit: float
+    experts: int
+    top: int
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+
+    @classmethod
+    def from_json(cls, m: Optional[dict]) -> Optional["ClampedMoEConfig"]:
+        if m is None:
+            return None
+        if m.get("kind", "moe") != "moe":
+            raise ValueError(f"unknown feed-forward kind {m.get('kind')!r}")
+        shared = m.get("shared") or {}
+        return cls(ff=int(m["expert"]["ff"]), limit=float(m["expert"]["limit"]), experts=int(m["router"]["experts"]),
+                   top=int(m["router"]["top"]), shared_ff=int(shared.get("ff", 0) or 0),
+                   shared_limit=float(shared.get("limit", 0.0) or 0.0))
+
+
+@dataclass
+class BatasunLayerConfig:
+    mixer_type: str                     # "latent_attention" | "mamba2"
+    mixer: Any                          # LatentAttentionConfig | StateSpaceConfig
+    mlp: Optional[ClampedMoEConfig]
+
+
+@dataclass
+class BatasunConfig:
+    """config.json of a Batasun model: `vocab`, `width`, `norm.eps`, `layers` (each with `type`, `mixer`, `mlp`).
+    Layers are latent-attention or state-space mixers in any order, each followed by a mixture of experts or by
+    nothing; norms sit on the sublayers' outputs only and have gains stored around zero."""
+    vocab_size: int
+    hidden_size: int
+    rms_norm_eps: float
+    layers: List[BatasunLayerConfig]
+    torch_dtype: Any = torch.bfloat16
+    max_position_embeddings: int = 1 << 30      # rotation angles are computed from the position: no table to outgrow
+    model_type: str = "batasun"
+    tie_word_embeddings: bool = False
+    raw: dict = field(default_factory=dict, repr=False)
+
+    @classmethod
+    def from_json(cls, c: dict) -> "BatasunConfig":
+        layers = []
+        for i, entry in enumerate(c["layers"]):
+            kind = entry["type"]
+            if kind == "latent_attention":
+                mixer = LatentAttentionConfig.from_json(entry["mixer"])
+            elif kind == "mamba2":
+                mixer = StateSpaceConfig.from_json(entry["mixer"])
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+            layers.append(BatasunLayerConfig(kind, mixer, ClampedMoEConfig.from_json(entry.get("mlp"))))
+        for i, lc in enumerate(layers):
+            j = lc.mixer.kv_from if lc.mixer_type == "latent_attention" else None
+            if j is None:
+                continue
+            if not (0 <= j < i) or layers[j].mixer_type != "latent_attention" or layers[j].mixer.kv_from is not None:
+                raise ValueError(f"layer {i}: kv_from {j} is not an earlier latent-attention layer with a latent of its own")
+            a, o = lc.mixer, layers[j].mixer
+            if (a.kv_rank, a.rot_dim, a.rot_base) != (o.kv_rank, o.rot_dim, o.rot_base):
+                raise ValueError(f"layer {i}: latent sizes differ from layer {j}'s")
+        return cls(vocab_size=int(c["vocab"]), hidden_size=int(c["width"]),
+                   rms_norm_eps=float((c.get("norm") or {}).get("eps", 1e-6)), layers=layers, raw=c)
+
+    # ---- the names the cache manager and the runner read from an HF config --------------------------
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layers)
+
+    @property
+    def num_key_value_heads(self) -> int:
+        return 1                    # the cached latent is shared by all heads
+
+    @property
+    def num_attention_heads(self) -> int:
+        return max([l.mixer.heads for l in self.layers if l.mixer_type == "latent_attention"] or [1])
+
+    @property
+    def head_dim(self) -> int:
+        return max([l.mixer.kv_rank + l.mixer.rot_dim for l in self.layers if l.mixer_type == "latent_attention"] or [1])
+
+
+ARCHITECTURES = {"Movolorn": MovolornConfig, "Batasun": BatasunConfig}
 
 
 def load_model_config(path: str):

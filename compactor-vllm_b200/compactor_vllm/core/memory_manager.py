@@ -123,7 +123,14 @@ class SlotMap:
             cache.free_batch(slot)
 
 
+class _SlotAnchor:
+    """Takes the cache views of a model without attention layers; nothing reads them."""
+    k_cache = v_cache = page_table = bh_seq_lens = page_size = None
+
+
 class KVCacheManager:
+    state_pool = None      # RecurrentStatePool of models with recurrent layers
+
     def __init__(self, rank: int, config: LLMConfig):
         hf = config.hf_config
         tp = dist.get_world_size() if dist.is_available() and dist.is_initialized() else config.tensor_parallel_size
@@ -172,8 +179,18 @@ class KVCacheManager:
         """Size the cache (unless `num_pages` is given), allocate it and hand every attention layer its views.
         device_allocator=True: the GPU-resident page allocator (same surface, same page ids)."""
         cache_type = DevicePagedKVCache if device_allocator else PagedKVCache
+        if hasattr(model, "state_layers"):      # recurrent layers: their state lives in slots beside the paged cache
+            from compactor_vllm.kv_cache.state_pool import RecurrentStatePool
+
+            self.state_pool = RecurrentStatePool(self.max_num_batches, self.model_dtype, f"cuda:{self.rank}")
+            for layer in model.state_layers():
+                self.state_pool.attach(layer)
         if hasattr(model, "cache_specs"):
-            return self._init_cache_from_specs(model.cache_specs(), num_pages, cache_type)
+            specs = model.cache_specs()
+            if not specs:     # no attention layer at all: a one-number cache layer keeps the slot bookkeeping in one place
+                self._slot_anchor = _SlotAnchor()
+                specs = [(self._slot_anchor, 1, 1, 0)]
+            return self._init_cache_from_specs(specs, num_pages, cache_type)
         if num_pages is None:
             num_pages = self.get_num_pages(self.gpu_frac, self.max_pages_per_batch)
         self.num_pages = int(num_pages)

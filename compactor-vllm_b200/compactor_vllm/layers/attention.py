@@ -129,8 +129,10 @@ class BiasedChunkAttention(nn.Module):
 
     def __init__(self, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, scale: float, *,
                  slopes: Optional[torch.Tensor] = None, chunk: int = 0, sink: bool = False, qk_norm: bool = False,
-                 eps: float = 1e-6):
+                 eps: float = 1e-6, values_in_keys: bool = False):
         super().__init__()
+        # values_in_keys: a value row is the first v_head_dim columns of its key row; there is no value cache
+        self.values_in_keys = bool(values_in_keys)
         self.num_heads, self.num_kv_heads = int(num_heads), int(num_kv_heads)
         self.head_dim, self.v_head_dim = int(head_dim), int(v_head_dim)
         self.scale, self.chunk, self.sink, self.eps = float(scale), int(chunk), bool(sink), float(eps)
@@ -176,21 +178,35 @@ class BiasedChunkAttention(nn.Module):
             N.ptr(qkv), qkv.stride(0), N.ptr(self.q_norm_weight), N.ptr(self.k_norm_weight), self.eps,
             N.ptr(ctx.positions_i32), N.ptr(ctx.token_slot), N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache),
             *table, N.ptr(self.bh_seq_lens), T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)), "cvllm_qknorm_store")
-        out = torch.empty((T, H, Dv), dtype=qkv.dtype, device=dev)
+        return self.attend(q)
+
+    def attend(self, q: torch.Tensor) -> torch.Tensor:
+        """q [T, H, D] (normed / rotated already, the step's keys in the cache) -> [T, H * Dv]."""
+        from compactor_vllm import _native as N
+
+        ctx: Context = get_context()
+        T = q.shape[0]
+        H, G, D, Dv = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        assert q.is_contiguous() and q.dtype == self.k_cache.dtype
+        dev, code, lib = q.device, N.block_dtype_code(q.dtype), N.lib()
+        pt = self.page_table
+        table = (N.ptr(pt), pt.stride(0), pt.stride(1), int(self.page_size))
+        v_cache, v_stride = (self.k_cache, D) if self.values_in_keys else (self.v_cache, Dv)
+        out = torch.empty((T, H, Dv), dtype=q.dtype, device=dev)
         if ctx.is_prefill:
             B = ctx.batch_mapping.numel()
             N.check(lib.cvllm_bias_attn_varlen(
-                N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache), *table, N.ptr(ctx.cu_seqlens_q),
+                N.ptr(q), N.ptr(self.k_cache), N.ptr(v_cache), *table, N.ptr(ctx.cu_seqlens_q),
                 N.ptr(ctx.seq_start), N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink),
                 self.scale, N.ptr(out), B, int(ctx.max_seqlen_q), H, G, D, Dv, T, self.k_cache.shape[0], pt.shape[-1],
-                code, N.stream(dev)), "cvllm_bias_attn_varlen")
+                v_stride, code, N.stream(dev)), "cvllm_bias_attn_varlen")
         else:
             assert ctx.batch_mapping.numel() == T
             splits = self.decode_splits(T, int(ctx.max_seqlen_k))
             ws = N.workspace(dev, 4 * T * H * splits * (2 + Dv), "bias_attn_decode") if splits > 1 else None
             N.check(lib.cvllm_bias_attn_decode(
-                N.ptr(q), N.ptr(self.k_cache), N.ptr(self.v_cache), *table, N.ptr(ctx.positions_i32),
+                N.ptr(q), N.ptr(self.k_cache), N.ptr(v_cache), *table, N.ptr(ctx.positions_i32),
                 N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), self.scale, N.ptr(out),
-                T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, code,
+                T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, v_stride, code,
                 N.stream(dev)), "cvllm_bias_attn_decode")
         return out.view(T, H * Dv)

@@ -53,14 +53,18 @@ class RMSNorm(nn.Module):
 
 
 def sandwich_norm(resid: torch.Tensor, *, branch: torch.Tensor | None = None, post_weight: torch.Tensor | None = None,
-                  pre_weight: torch.Tensor | None = None, eps: float = 1e-6, out_dtype: torch.dtype | None = None):
+                  pre_weight: torch.Tensor | None = None, eps: float = 1e-6, out_dtype: torch.dtype | None = None,
+                  gain_offset: float = 0.0, assign: bool = False, cast_out: bool = False):
     """One launch of `cvllm_sandwich_norm` on a 32-bit residual stream `resid` [T, width], updated IN PLACE:
 
-        branch given:      resid += branch / sqrt(mean(branch^2) + eps) * post_weight
-        pre_weight given:  returns  resid / sqrt(mean(resid^2) + eps) * pre_weight  in `out_dtype`
+        branch given:      resid += branch / sqrt(mean(branch^2) + eps) * (post_weight + gain_offset)
+                           (`assign`: resid = that, without the sum - the norm of an embedding that starts the stream)
+        pre_weight given:  returns  resid / sqrt(mean(resid^2) + eps) * (pre_weight + gain_offset)  in `out_dtype`
+        cast_out:          returns  resid itself rounded to `out_dtype` (models whose sublayers read the stream unnormed)
 
     i.e. the post-norm of one sublayer's output, the residual sum and the pre-norm of the next sublayer.  Statistics,
-    sum and residual are fp32 whatever the activations' dtype; the weights are fp32 tensors."""
+    sum and residual are fp32 whatever the activations' dtype; the weights are fp32 tensors (`gain_offset` 1 for
+    gains stored around zero)."""
     assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.stride(1) == 1
     rows, width = resid.shape
     y_code = o_code = N.CVLLM_F32
@@ -69,13 +73,15 @@ def sandwich_norm(resid: torch.Tensor, *, branch: torch.Tensor | None = None, po
     if branch is not None:
         assert branch.shape == resid.shape and branch.stride(1) == 1 and post_weight.dtype == torch.float32
         y_code, y_stride = N.block_dtype_code(branch.dtype), branch.stride(0)
-    if pre_weight is not None:
-        assert pre_weight.dtype == torch.float32
+    assert pre_weight is None or not cast_out
+    if pre_weight is not None or cast_out:
+        assert pre_weight is None or pre_weight.dtype == torch.float32
         out = torch.empty((rows, width), dtype=out_dtype or torch.float32, device=resid.device)
         o_code, o_stride = N.block_dtype_code(out.dtype), out.stride(0)
     rc = N.lib().cvllm_sandwich_norm(
         N.ptr(branch), y_stride, y_code, N.ptr(post_weight) if branch is not None else None, N.ptr(resid),
-        resid.stride(0), N.ptr(pre_weight), N.ptr(out), o_stride, o_code, rows, width, float(eps), N.stream(resid.device))
+        resid.stride(0), N.ptr(pre_weight), N.ptr(out), o_stride, o_code, rows, width, float(eps), float(gain_offset),
+        int(bool(assign)), N.stream(resid.device))
     N.check(rc, "cvllm_sandwich_norm")
     return out
 

@@ -35,14 +35,15 @@ struct PagedKV {
   int64_t table_stride_slot, table_stride_head;
   int page_size;
   int page_shift;           // log2(page_size) when that is a power of two, else -1
+  int64_t v_stride;         // elements between value rows (Dv, or more when the values are columns of wider rows)
 };
 
 inline PagedKV make_paged(const void* k, const void* v, const int32_t* table, int64_t stride_slot, int64_t stride_head,
-                          int page_size) {
+                          int page_size, int64_t v_stride) {
   int shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (shift = 0; (1 << shift) < page_size; ++shift) {}
-  return PagedKV{k, v, table, stride_slot, stride_head, page_size, shift};
+  return PagedKV{k, v, table, stride_slot, stride_head, page_size, shift, v_stride};
 }
 
 __device__ __forceinline__ int64_t cache_row(const PagedKV& c, int slot, int g, int pos) {
@@ -154,7 +155,7 @@ __global__ void __launch_bounds__(256) bias_attn_varlen_kernel(
     }
     for (int i = tid; i < BN * Dv; i += 256) {
       const int r = i / Dv, d = i - r * Dv;
-      Vs[i] = r < nk ? to_f<T>(vc[rix[r] * Dv + d]) : 0.f;
+      Vs[i] = r < nk ? to_f<T>(vc[rix[r] * c.v_stride + d]) : 0.f;
     }
     __syncthreads();
     float s[4][NJ];
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(128) bias_attn_varlen_mma_kernel(
     for (int i = tid; i < BN * (DMAX / 8); i += 128) {   // every column of the tile: unused ones must not hold NaN
       const int r = i / (DMAX / 8), cv = i - r * (DMAX / 8);
       const bool in = r < nk && cv < vvec;
-      cp_async16(&Vs[stage][r][cv * 8], in ? vc + cache_row(c, slot, g, k0 + r) * Dv + cv * 8 : vc, in ? 16 : 0);
+      cp_async16(&Vs[stage][r][cv * 8], in ? vc + cache_row(c, slot, g, k0 + r) * c.v_stride + cv * 8 : vc, in ? 16 : 0);
     }
     cp_async_commit();
   };
@@ -531,7 +532,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
     for (int j = 0; j < nk; ++j) {
       const float pj_w = __shfl_sync(0xffffffffu, p, j);
       const int64_t rj = __shfl_sync(0xffffffffu, row, j);
-      const T* vr = vc + rj * Dv;
+      const T* vr = vc + rj * c.v_stride;
 #pragma unroll
       for (int cc = 0; cc < kDecCols; ++cc) {
         const int col = lane + 32 * cc;
@@ -744,7 +745,7 @@ __global__ void __launch_bounds__(128) bias_attn_decode_split_kernel(
 #pragma unroll
         for (int pc = 0; pc < kPieces; ++pc) {
           if (cb < D) cp_async16(ring_at(stage, 0, i, pc), kc + row * D + cb + pc * kVec, 16);
-          if (cb < Dv) cp_async16(ring_at(stage, 1, i, pc), vc + row * Dv + cb + pc * kVec, 16);
+          if (cb < Dv) cp_async16(ring_at(stage, 1, i, pc), vc + row * c.v_stride + cb + pc * kVec, 16);
         }
       }
     }
@@ -999,7 +1000,7 @@ extern "C" int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const flo
   if (T == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(qkv && positions && token_slot && q_out && k_cache && v_cache && page_table && check_dtype(dtype));
   auto st = static_cast<cudaStream_t>(stream);
-  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
+  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size, Dv);
   const int64_t align = dtype == CVLLM_BF16 ? 8 : 4;
   if (D % 8 == 0 && Dv % 8 == 0 && D <= 256 && Dv <= 256 && qkv_stride % align == 0 && aligned16(qkv) &&
       aligned16(q_out) && aligned16(k_cache) && aligned16(v_cache)) {
@@ -1041,15 +1042,18 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
                                       int page_size, const int32_t* cu_seqlens_q, const int32_t* seq_start,
                                       const int32_t* batch_mapping, const float* slopes, int chunk, int sink,
                                       float scale, void* out, int B, int max_new, int H, int G, int D, int Dv,
-                                      int total_tokens, int64_t cache_rows, int pages_per_head, int dtype,
-                                      cvllm_stream_t stream) {
+                                      int total_tokens, int64_t cache_rows, int pages_per_head, int64_t v_stride,
+                                      int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0);
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && cu_seqlens_q && seq_start && batch_mapping && out &&
                   check_dtype(dtype) && page_size > 0);
   CVLLM_CHECK_SUPPORTED(Dv <= 256 && B <= 65535 && H <= 65535);
+  CVLLM_CHECK_ARG(v_stride == 0 || v_stride >= Dv);
+  if (v_stride == 0) v_stride = Dv;
   auto st = static_cast<cudaStream_t>(stream);
-  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
+  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size, v_stride);
+  const int64_t vec = dtype == CVLLM_BF16 ? 8 : 4;   // elements per 16-byte copy
   const int dvc = cdiv(Dv, 16);
   const float fs = sink ? 1.f : 0.f;
   const size_t cap = 226 * 1024;  // + the static row-index array
@@ -1060,12 +1064,14 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
   return dispatch_dvc<T, BN>(dvc, q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B, \
                              max_new, H, G, D, Dv, st)
   const int path = test_options().bias_attn_fma.load();   // 0 product, 1 fp32 FMA kernel, 2 no tcgen05 kernel
-  if (dtype == CVLLM_BF16 && D == 128 && Dv == 128 && page_size % 128 == 0 && (H / G) % 2 == 0 && path == 0 &&
+  if (dtype == CVLLM_BF16 && D == 128 && Dv == 128 && v_stride == Dv && page_size % 128 == 0 && (H / G) % 2 == 0 &&
+      path == 0 &&
       table_stride_head == pages_per_head && table_stride_slot == (int64_t)G * pages_per_head && cache_rows > 0)
     return cvllm_launch_prefill_bias(q, k_cache, v_cache, cache_rows, out, seq_start, slopes, page_table,
                                      batch_mapping, cu_seqlens_q, B, total_tokens, H, G, page_size, pages_per_head,
                                      max_new, scale, chunk, sink, st);
-  if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && path != 1) {
+  if (dtype == CVLLM_BF16 && D % 16 == 0 && Dv % 8 == 0 && D <= 128 && Dv <= 128 && path != 1 &&
+      v_stride % vec == 0 && aligned16(k_cache) && aligned16(v_cache)) {
     if (D <= 64 && Dv <= 64)
       return launch_varlen_mma<64>(q, c, cu_seqlens_q, seq_start, batch_mapping, slopes, chunk, fs, scale, out, B,
                                    max_new, H, G, D, Dv, st);
@@ -1086,15 +1092,18 @@ extern "C" int cvllm_bias_attn_decode(const void* q, const void* k_cache, const 
                                       int page_size, const int32_t* positions, const int32_t* batch_mapping,
                                       const float* slopes, int chunk, int sink, float scale, void* out, int B, int H,
                                       int G, int D, int Dv, int reserved_slot, int splits, float* workspace,
-                                      size_t workspace_bytes, int dtype, cvllm_stream_t stream) {
+                                      size_t workspace_bytes, int64_t v_stride, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(B >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Dv > 0 && chunk >= 0 && splits >= 1);
   if (B == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && positions && batch_mapping && out && check_dtype(dtype) &&
                   page_size > 0);
   CVLLM_CHECK_SUPPORTED(Dv <= 32 * kDecCols && H <= 65535 && B <= 65535);
+  CVLLM_CHECK_ARG(v_stride == 0 || v_stride >= Dv);
+  if (v_stride == 0) v_stride = Dv;
   auto st = static_cast<cudaStream_t>(stream);
-  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size);
-  if (D % 8 == 0 && Dv % 8 == 0 && D <= 256 && Dv <= 256) {
+  const PagedKV c = make_paged(k_cache, v_cache, page_table, table_stride_slot, table_stride_head, page_size, v_stride);
+  if (D % 8 == 0 && Dv % 8 == 0 && D <= 256 && Dv <= 256 && v_stride % 8 == 0 && aligned16(k_cache) &&
+      aligned16(v_cache)) {
     if (splits > 1) {
       CVLLM_CHECK_ARG(workspace != nullptr);
       if (workspace_bytes < sizeof(float) * (size_t)B * H * splits * (2 + Dv)) {

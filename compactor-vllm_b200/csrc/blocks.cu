@@ -39,13 +39,14 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // One CTA per row.  row (dynamic shared memory) holds the row in fp32 between the passes.
-//   y != NULL:      resid += y / sqrt(mean(y^2) + eps) * w_post
-//   w_pre != NULL:  out = resid / sqrt(mean(resid^2) + eps) * w_pre
+//   y != NULL:      resid (+)= y / sqrt(mean(y^2) + eps) * (w_post + gain_offset)      ('=' when assign is set)
+//   w_pre != NULL:  out = resid / sqrt(mean(resid^2) + eps) * (w_pre + gain_offset)
+//   out != NULL and w_pre == NULL:  out = resid, rounded to the output type
 template <typename TY, typename TO>
 __global__ void __launch_bounds__(kThreads) sandwich_norm_kernel(
     const TY* __restrict__ y, int64_t y_stride, const float* __restrict__ w_post, float* __restrict__ resid,
     int64_t r_stride, const float* __restrict__ w_pre, TO* __restrict__ out, int64_t o_stride, int width,
-    float eps) {
+    float eps, float gain_offset, int assign) {
   extern __shared__ float row[];
   __shared__ float red[kThreads / 32];
   const int64_t r = blockIdx.x;
@@ -61,20 +62,25 @@ __global__ void __launch_bounds__(kThreads) sandwich_norm_kernel(
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     for (int i = threadIdx.x; i < width; i += kThreads) {
-      const float v = res[i] + row[i] * inv * w_post[i];
+      const float nv = row[i] * inv * (w_post[i] + gain_offset);
+      const float v = assign ? nv : res[i] + nv;
       res[i] = v;
       row[i] = v;
     }
   } else {
     for (int i = threadIdx.x; i < width; i += kThreads) row[i] = res[i];
   }
-  if (w_pre == nullptr) return;
+  if (out == nullptr) return;
+  TO* o = out + r * o_stride;
+  if (w_pre == nullptr) {   // every thread reads back what it wrote itself
+    for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i]);
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < width; i += kThreads) ss += row[i] * row[i];
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-  TO* o = out + r * o_stride;
-  for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i] * inv * w_pre[i]);
+  for (int i = threadIdx.x; i < width; i += kThreads) o[i] = from_f<TO>(row[i] * inv * (w_pre[i] + gain_offset));
 }
 
 __device__ __forceinline__ float act_silu(float z) { return z / (1.0f + expf(-z)); }
@@ -82,10 +88,23 @@ __device__ __forceinline__ float act_gelu_tanh(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// out[t, f] = act(x[t, f]) * x[t, F + f]
+// KIND 2, the clamped gated unit: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1)
+__device__ __forceinline__ float act_clamped_glu(float g, float u, float limit) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+template <int KIND>
+__device__ __forceinline__ float gated(float g, float u, float limit) {
+  if constexpr (KIND == 0) return act_silu(g) * u;
+  else if constexpr (KIND == 1) return act_gelu_tanh(g) * u;
+  else return act_clamped_glu(g, u, limit);
+}
+
+// out[t, f] = act(x[t, f]) * x[t, F + f]   (KIND 0 silu, 1 tanh gelu; 2 the clamped gated unit)
 template <typename T, int KIND>
 __global__ void gated_act_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ out,
-                                 int64_t o_stride, int64_t rows, int F) {
+                                 int64_t o_stride, int64_t rows, int F, float limit) {
   const int64_t total = rows * (int64_t)F;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
@@ -93,15 +112,14 @@ __global__ void gated_act_kernel(const T* __restrict__ x, int64_t x_stride, T* _
     const int f = (int)(i - t * F);
     const float g = to_f<T>(x[t * x_stride + f]);
     const float u = to_f<T>(x[t * x_stride + F + f]);
-    const float a = KIND == 0 ? act_silu(g) : act_gelu_tanh(g);
-    out[t * o_stride + f] = from_f<T>(a * u);
+    out[t * o_stride + f] = from_f<T>(gated<KIND>(g, u, limit));
   }
 }
 
 // the same, eight elements per thread with 16-byte loads (F and both strides multiples of 8, 16-byte aligned bases)
 template <typename T, int KIND>
 __global__ void gated_act_vec_kernel(const T* __restrict__ x, int64_t x_stride, T* __restrict__ out,
-                                     int64_t o_stride, int64_t rows, int F) {
+                                     int64_t o_stride, int64_t rows, int F, float limit) {
   const int F8 = F / 8;
   const int64_t total = rows * (int64_t)F8;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
@@ -124,8 +142,8 @@ __global__ void gated_act_vec_kernel(const T* __restrict__ x, int64_t x_stride, 
       uint32_t r[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const float lo = (KIND == 0 ? act_silu(g[2 * k]) : act_gelu_tanh(g[2 * k])) * u[2 * k];
-        const float hi = (KIND == 0 ? act_silu(g[2 * k + 1]) : act_gelu_tanh(g[2 * k + 1])) * u[2 * k + 1];
+        const float lo = gated<KIND>(g[2 * k], u[2 * k], limit);
+        const float hi = gated<KIND>(g[2 * k + 1], u[2 * k + 1], limit);
         r[k] = pack2<true>(lo, hi);
       }
       *reinterpret_cast<uint4*>(op) = make_uint4(r[0], r[1], r[2], r[3]);
@@ -136,7 +154,7 @@ __global__ void gated_act_vec_kernel(const T* __restrict__ x, int64_t x_stride, 
         u[k] = to_f<T>(gp[F + k]);
       }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) op[k] = from_f<T>((KIND == 0 ? act_silu(g[k]) : act_gelu_tanh(g[k])) * u[k]);
+      for (int k = 0; k < 8; ++k) op[k] = from_f<T>(gated<KIND>(g[k], u[k], limit));
     }
   }
 }
@@ -162,12 +180,13 @@ __device__ __forceinline__ int warp_argmax(const float* v, int n, float* best_ou
 
 constexpr int kRouteWarps = 4;
 
-// One warp per token.  s = softmax(logits); choice = s + correction; experts outside the `keep` groups with
+// One warp per token.  mode 0: s = softmax(logits); choice = s + correction; experts outside the `keep` groups with
 // the largest group maximum of choice are struck; the `top` largest remaining choices are taken, each with
-// its plain s as weight.  Shared memory per warp: s[E], choice[E], group maxima[groups].
+// its plain s as weight.  mode 1: the `top` largest LOGITS are taken (lowest index first among equals) and the
+// weights are the softmax over the chosen logits alone.  Shared memory per warp: s[E], choice[E], group maxima[groups].
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
     const float* __restrict__ logits, int64_t l_stride, const float* __restrict__ correction, int T, int E,
-    int top, int groups, int keep, int32_t* __restrict__ idx, float* __restrict__ wts) {
+    int top, int groups, int keep, int mode, int32_t* __restrict__ idx, float* __restrict__ wts) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
@@ -176,6 +195,27 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
   float* c = s + E;
   float* gm = c + E;
   const float* z = logits + (int64_t)t * l_stride;
+  if (mode == 1) {
+    for (int e = lane; e < E; e += 32) c[e] = z[e];
+    __syncwarp();
+    float zmax = 0.f, sum = 0.f;
+    for (int r = 0; r < top; ++r) {
+      float b;
+      const int e = warp_argmax(c, E, &b);
+      __syncwarp();
+      if (r == 0) zmax = b;               // the first choice is the largest logit
+      const float p = expf(b - zmax);
+      sum += p;
+      if (lane == 0) {
+        idx[(int64_t)t * top + r] = e;
+        wts[(int64_t)t * top + r] = p;
+        c[e] = NAN;
+      }
+      __syncwarp();
+    }
+    if (lane < top) wts[(int64_t)t * top + lane] /= sum;   // top <= 32 in this mode (checked by the host)
+    return;
+  }
   float m = -INFINITY;
   for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
   m = warp_max(m);
@@ -225,19 +265,22 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
   }
 }
 
-// out[t, :] = sum_r w[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :])  (+ shared[t, :]),  fp32 sums.
+// out[t, :] = sum_r w[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :])  (+ s_t shared[t, :]),  fp32 sums.
 // pos maps a (token, choice) pair to its row of y (the pairs sorted by expert); NULL = the pair's own index.
+// s_t = sigmoid(shared_gate[t * gate_stride]) when shared_gate is given (one logit per token), else 1.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ pos,
                                    const float* __restrict__ w, int top,
                                    const int32_t* __restrict__ idx, int n_real, const T* __restrict__ h,
-                                   const T* __restrict__ shared, float* __restrict__ out, int64_t rows, int width) {
+                                   const T* __restrict__ shared, const float* __restrict__ shared_gate,
+                                   int64_t gate_stride, float* __restrict__ out, int64_t rows, int width) {
   const int64_t total = rows * (int64_t)width;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / width;
     const int c = (int)(i - t * width);
     float acc = shared ? to_f<T>(shared[i]) : 0.f;
+    if (shared && shared_gate) acc *= 1.0f / (1.0f + expf(-shared_gate[t * gate_stride]));
     for (int r = 0; r < top; ++r) {
       const float wr = w[t * top + r];
       if (idx[t * top + r] >= n_real)
@@ -258,7 +301,8 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __res
 template <typename T, bool GATED, int KIND>
 __global__ void __launch_bounds__(256) expert_gemv_kernel(const T* __restrict__ xs, int x_div,
                                                           const T* __restrict__ w, const int32_t* __restrict__ idx,
-                                                          int n_real, T* __restrict__ out, int N, int K) {
+                                                          int n_real, T* __restrict__ out, int N, int K,
+                                                          float limit) {
   const int p = blockIdx.y;
   const int e = idx[p];
   if (e >= n_real) return;
@@ -280,7 +324,7 @@ __global__ void __launch_bounds__(256) expert_gemv_kernel(const T* __restrict__ 
     // the library GEMM path rounds gate and up to the storage type before the activation; do the same
     a = to_f<T>(from_f<T>(a));
     b = to_f<T>(from_f<T>(b));
-    a = (KIND == 0 ? act_silu(a) : act_gelu_tanh(a)) * b;
+    a = gated<KIND>(a, b, limit);
   }
   if (lane == 0) out[(int64_t)p * N + n] = from_f<T>(a);
 }
@@ -292,11 +336,13 @@ using namespace cvllm;
 
 extern "C" int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype, const float* w_post, float* resid,
                                    int64_t r_stride, const float* w_pre, void* out, int64_t o_stride,
-                                   int out_dtype, int rows, int width, float eps, cvllm_stream_t stream) {
+                                   int out_dtype, int rows, int width, float eps, float gain_offset, int assign,
+                                   cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(rows >= 0 && width > 0 && resid);
   if (rows == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG((y == nullptr) == (w_post == nullptr));
-  CVLLM_CHECK_ARG((w_pre == nullptr) == (out == nullptr));
+  CVLLM_CHECK_ARG(w_pre == nullptr || out != nullptr);
+  CVLLM_CHECK_ARG(!assign || y != nullptr);
   CVLLM_CHECK_ARG(y == nullptr || y_dtype == CVLLM_BF16 || y_dtype == CVLLM_F32);
   CVLLM_CHECK_ARG(out == nullptr || out_dtype == CVLLM_BF16 || out_dtype == CVLLM_F32);
   CVLLM_CHECK_SUPPORTED(width <= 12288);
@@ -306,7 +352,7 @@ extern "C" int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype,
 #define CVLLM_SANDWICH(TY, TO)                                                                                 \
   sandwich_norm_kernel<TY, TO><<<rows, kThreads, smem, st>>>(static_cast<const TY*>(y), y_stride, w_post,      \
                                                              resid, r_stride, w_pre, static_cast<TO*>(out),    \
-                                                             o_stride, width, eps)
+                                                             o_stride, width, eps, gain_offset, assign)
   if (yb && ob) CVLLM_SANDWICH(__nv_bfloat16, __nv_bfloat16);
   else if (yb) CVLLM_SANDWICH(__nv_bfloat16, float);
   else if (ob) CVLLM_SANDWICH(float, __nv_bfloat16);
@@ -317,8 +363,8 @@ extern "C" int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype,
 }
 
 extern "C" int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F,
-                               int kind, int dtype, cvllm_stream_t stream) {
-  CVLLM_CHECK_ARG(rows >= 0 && F > 0 && (kind == 0 || kind == 1));
+                               int kind, float limit, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(rows >= 0 && F > 0 && kind >= 0 && kind <= 2);
   if (rows == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(x && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
   auto st = static_cast<cudaStream_t>(stream);
@@ -328,14 +374,16 @@ extern "C" int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64
 #define CVLLM_GATED(T, K)                                                                                      \
   if (vec)                                                                                                     \
     gated_act_vec_kernel<T, K><<<(grid + 7) / 8, 256, 0, st>>>(static_cast<const T*>(x), x_stride,             \
-                                                               static_cast<T*>(out), o_stride, rows, F);       \
+                                                               static_cast<T*>(out), o_stride, rows, F, limit); \
   else                                                                                                         \
     gated_act_kernel<T, K><<<grid, 256, 0, st>>>(static_cast<const T*>(x), x_stride, static_cast<T*>(out),     \
-                                                 o_stride, rows, F)
+                                                 o_stride, rows, F, limit)
   if (dtype == CVLLM_BF16) {
-    if (kind == 0) { CVLLM_GATED(__nv_bfloat16, 0); } else { CVLLM_GATED(__nv_bfloat16, 1); }
+    if (kind == 0) { CVLLM_GATED(__nv_bfloat16, 0); } else if (kind == 1) { CVLLM_GATED(__nv_bfloat16, 1); }
+    else { CVLLM_GATED(__nv_bfloat16, 2); }
   } else {
-    if (kind == 0) { CVLLM_GATED(float, 0); } else { CVLLM_GATED(float, 1); }
+    if (kind == 0) { CVLLM_GATED(float, 0); } else if (kind == 1) { CVLLM_GATED(float, 1); }
+    else { CVLLM_GATED(float, 2); }
   }
 #undef CVLLM_GATED
   CVLLM_CHECK_LAUNCH();
@@ -343,8 +391,10 @@ extern "C" int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64
 }
 
 extern "C" int cvllm_moe_route(const float* logits, int64_t l_stride, const float* correction, int T, int E, int top,
-                               int groups, int keep, int32_t* idx, float* wts, cvllm_stream_t stream) {
+                               int groups, int keep, int mode, int32_t* idx, float* wts, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(T >= 0 && E > 0 && top > 0 && top <= E && groups > 0 && keep > 0 && keep <= groups);
+  CVLLM_CHECK_ARG(mode == 0 || (mode == 1 && groups == 1 && correction == nullptr));
+  CVLLM_CHECK_SUPPORTED(mode == 0 || top <= 32);
   if (T == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(logits && idx && wts && E % groups == 0 && keep * (E / groups) >= top);
   CVLLM_CHECK_SUPPORTED(E <= 2048);
@@ -354,14 +404,14 @@ extern "C" int cvllm_moe_route(const float* logits, int64_t l_stride, const floa
   if (smem > 48 * 1024)
     CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(route_kernel), (int)smem, mask));
   route_kernel<<<cdiv(T, kRouteWarps), kRouteWarps * 32, smem, st>>>(logits, l_stride, correction, T, E, top,
-                                                                    groups, keep, idx, wts);
+                                                                    groups, keep, mode, idx, wts);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }
 
 extern "C" int cvllm_moe_combine(const void* y, const int32_t* pos, const float* w, int top, const int32_t* idx, int n_real,
-                                 const void* h, const void* shared, float* out, int64_t rows, int width, int dtype,
-                                 cvllm_stream_t stream) {
+                                 const void* h, const void* shared, const float* shared_gate, int64_t gate_stride,
+                                 float* out, int64_t rows, int width, int dtype, cvllm_stream_t stream) {
   CVLLM_CHECK_ARG(rows >= 0 && width > 0 && top > 0);
   if (rows == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(y && w && idx && h && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
@@ -371,18 +421,19 @@ extern "C" int cvllm_moe_combine(const void* y, const int32_t* pos, const float*
   if (dtype == CVLLM_BF16)
     moe_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(y), pos, w, top, idx, n_real, static_cast<const __nv_bfloat16*>(h),
-        static_cast<const __nv_bfloat16*>(shared), out, rows, width);
+        static_cast<const __nv_bfloat16*>(shared), shared_gate, gate_stride, out, rows, width);
   else
     moe_combine_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(y), pos, w, top, idx, n_real,
                                                     static_cast<const float*>(h), static_cast<const float*>(shared),
-                                                    out, rows, width);
+                                                    shared_gate, gate_stride, out, rows, width);
   CVLLM_CHECK_LAUNCH();
   return CVLLM_OK;
 }
 
 extern "C" int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const int32_t* idx, int n_real, void* out,
-                                 int pairs, int N, int K, int gated_kind, int dtype, cvllm_stream_t stream) {
-  CVLLM_CHECK_ARG(pairs >= 0 && N > 0 && K > 0 && x_div > 0 && gated_kind >= -1 && gated_kind <= 1);
+                                 int pairs, int N, int K, int gated_kind, float limit, int dtype,
+                                 cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(pairs >= 0 && N > 0 && K > 0 && x_div > 0 && gated_kind >= -1 && gated_kind <= 2);
   if (pairs == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(xs && w && idx && out && (dtype == CVLLM_BF16 || dtype == CVLLM_F32));
   CVLLM_CHECK_SUPPORTED(pairs <= 65535);
@@ -390,15 +441,17 @@ extern "C" int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const
   dim3 grid(cdiv(N, 8), pairs);
 #define CVLLM_GEMV(T, G, KD)                                                                                   \
   expert_gemv_kernel<T, G, KD><<<grid, 256, 0, st>>>(static_cast<const T*>(xs), x_div, static_cast<const T*>(w), \
-                                                     idx, n_real, static_cast<T*>(out), N, K)
+                                                     idx, n_real, static_cast<T*>(out), N, K, limit)
   if (dtype == CVLLM_BF16) {
     if (gated_kind < 0) CVLLM_GEMV(__nv_bfloat16, false, 0);
     else if (gated_kind == 0) CVLLM_GEMV(__nv_bfloat16, true, 0);
-    else CVLLM_GEMV(__nv_bfloat16, true, 1);
+    else if (gated_kind == 1) CVLLM_GEMV(__nv_bfloat16, true, 1);
+    else CVLLM_GEMV(__nv_bfloat16, true, 2);
   } else {
     if (gated_kind < 0) CVLLM_GEMV(float, false, 0);
     else if (gated_kind == 0) CVLLM_GEMV(float, true, 0);
-    else CVLLM_GEMV(float, true, 1);
+    else if (gated_kind == 1) CVLLM_GEMV(float, true, 1);
+    else CVLLM_GEMV(float, true, 2);
   }
 #undef CVLLM_GEMV
   CVLLM_CHECK_LAUNCH();

@@ -1,0 +1,353 @@
+// Selective state-space mixer (the scalar-decay, multi-head form): per head h with state S [P, N] (P value
+// channels, N state channels; head h reads the B / C rows of group h / (heads / groups)):
+//     dt_t = softplus(dt_raw_t + dt_bias_h)          S_t = exp(-exp(A_log_h) dt_t) S_(t-1) + dt_t x_t B_t^T
+//     y_t  = S_t C_t + D_h x_t
+// in front of it a short causal convolution per channel with silu, behind it a gate silu(z) and an RMS norm in equal
+// parts.  A sequence's state - S in fp32 and the last taps - 1 inputs of the convolution - lives in a slot of a state
+// pool and is carried from step to step; a step brings, per sequence, any number of new tokens (a portion of a prompt
+// or one decoded token).  A portion that starts at position 0 starts from a zero state whatever the slot holds, so a
+// slot needs no clearing when it is handed to another sequence.
+//   cvllm_causal_conv        out = silu(bias + sum_k w[:, k] * input(t - (taps - 1 - k))), fp32 out
+//   cvllm_conv_state_update  the slot's last taps - 1 inputs after the step
+//   cvllm_ssm_scan           the recurrence over the step's tokens, state read and written in place
+//   cvllm_gated_group_norm   out = unit_norm_per_part(y * silu(z)) * weight
+// Geometry of a step: cu_q [B + 1] token offsets and seq_start [B] first positions of the portions, batch_mapping [B]
+// slots; cu_q == NULL means one token per sequence at positions[b] (decode steps, CUDA-graph replays).
+// Everything but the stored projections is fp32.
+#include "common.cuh"
+
+namespace cvllm {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+struct StepGeom {
+  const int32_t* cu_q;        // [B + 1] or NULL
+  const int32_t* seq_start;   // [B] (with cu_q)
+  const int32_t* positions;   // [B] (without cu_q)
+  const int32_t* slots;       // [B]
+};
+
+__device__ __forceinline__ void portion(const StepGeom& g, int b, int& t0, int& n_new, int& start) {
+  if (g.cu_q) {
+    t0 = g.cu_q[b];
+    n_new = g.cu_q[b + 1] - t0;
+    start = g.seq_start[b];
+  } else {
+    t0 = b;
+    n_new = 1;
+    start = g.positions[b];
+  }
+}
+
+constexpr int kMaxTaps = 16;
+constexpr int kConvTokens = 8;   // tokens per CTA of the convolution
+
+// grid (token tiles, B, channel tiles), 128 threads = 128 channels.  x = columns x_off .. x_off + C of proj.
+// conv_state [slots, taps - 1, C]: entry s is the input at position start - (taps - 1) + s.
+template <typename T>
+__global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ proj, int64_t p_stride, int x_off, int C,
+                                                          int taps, const float* __restrict__ w,
+                                                          const float* __restrict__ bias,
+                                                          const T* __restrict__ conv_state, StepGeom g,
+                                                          float* __restrict__ out, int64_t o_stride) {
+  const int b = blockIdx.y;
+  int t0, n_new, start;
+  portion(g, b, t0, n_new, start);
+  const int j0 = blockIdx.x * kConvTokens;
+  if (j0 >= n_new) return;
+  const int ch = blockIdx.z * 128 + threadIdx.x;
+  if (ch >= C) return;
+  const int slot = g.slots[b];
+  float wk[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) wk[k] = k < taps ? w[(int64_t)ch * taps + k] : 0.f;
+  const float bv = bias ? bias[ch] : 0.f;
+  const T* st = conv_state + (int64_t)slot * (taps - 1) * C + ch;
+  const int j1 = min(j0 + kConvTokens, n_new);
+  for (int j = j0; j < j1; ++j) {
+    float acc = bv;
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) {
+      if (k < taps) {
+        const int src = j - (taps - 1 - k);
+        float v = 0.f;
+        if (src >= 0) v = to_f<T>(proj[(int64_t)(t0 + src) * p_stride + x_off + ch]);
+        else if (start + src >= 0) v = to_f<T>(st[(int64_t)(taps - 1 + src) * C]);   // start > 0: the slot's state
+        acc = fmaf(wk[k], v, acc);
+      }
+    }
+    out[(int64_t)(t0 + j) * o_stride + ch] = silu_f(acc);
+  }
+}
+
+// grid (B, channel tiles), 128 threads: a thread reads what it needs of its channel's old state, then writes the new.
+template <typename T>
+__global__ void __launch_bounds__(128) conv_state_update_kernel(const T* __restrict__ proj, int64_t p_stride,
+                                                                int x_off, int C, int taps,
+                                                                T* __restrict__ conv_state, StepGeom g,
+                                                                int reserved_slot) {
+  const int b = blockIdx.x;
+  const int ch = blockIdx.y * 128 + threadIdx.x;
+  if (ch >= C) return;
+  int t0, n_new, start;
+  portion(g, b, t0, n_new, start);
+  const int slot = g.slots[b];
+  if (slot == reserved_slot || n_new <= 0) return;
+  T* st = conv_state + (int64_t)slot * (taps - 1) * C + ch;
+  T keep[kMaxTaps];
+#pragma unroll
+  for (int s = 0; s < kMaxTaps - 1; ++s) {
+    if (s < taps - 1) {
+      const int j = n_new - (taps - 1) + s;   // index among the new tokens of the input that entry s will hold
+      if (j >= 0) keep[s] = proj[(int64_t)(t0 + j) * p_stride + x_off + ch];
+      else if (start + j >= 0) keep[s] = st[(int64_t)(s + n_new) * C];
+      else keep[s] = from_f<T>(0.f);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < kMaxTaps - 1; ++s)
+    if (s < taps - 1) st[(int64_t)s * C] = keep[s];
+}
+
+constexpr int kScanTokens = 16;   // tokens staged per pass
+constexpr int kNPT = 16;          // state channels per thread
+
+// grid (heads, B, value tiles), 256 threads = PT value channels x NS slices of the state dimension (NS a power of two,
+// NS * 16 >= N, PT = 256 / NS).  Thread (p, s) keeps S[p, 16 s .. 16 s + 15] in registers over the whole portion.
+// xbc [T, inner + 2 G N] fp32 = conv output (x | B | C); dt_raw = column dt_off + h of proj.
+template <typename T>
+__global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__ xbc, int64_t x_stride,
+                                                       const T* __restrict__ proj, int64_t p_stride, int dt_off,
+                                                       const float* __restrict__ dt_bias,
+                                                       const float* __restrict__ A_log, const float* __restrict__ Dp,
+                                                       float* __restrict__ state, StepGeom g, float* __restrict__ y,
+                                                       int64_t y_stride, int heads, int groups, int P, int N, int NS,
+                                                       int reserved_slot) {
+  extern __shared__ float sm[];
+  const int PT = 256 / NS;
+  const int NL = NS * (kNPT + 1);               // padded row of B / C: slice s starts at s * 17
+  float* Bs = sm;                               // [kScanTokens][NL]
+  float* Cs = Bs + kScanTokens * NL;            // [kScanTokens][NL]
+  float* xs = Cs + kScanTokens * NL;            // [kScanTokens][PT]
+  float* ys = xs + kScanTokens * PT;            // [kScanTokens][PT]
+  float* dts = ys + kScanTokens * PT;           // [kScanTokens]
+  float* dAs = dts + kScanTokens;               // [kScanTokens]
+  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * PT;
+  int t0, n_new, start;
+  portion(g, b, t0, n_new, start);
+  if (n_new <= 0) return;
+  const int slot = g.slots[b];
+  const int tid = threadIdx.x, s = tid & (NS - 1), pl = tid / NS, p = p0 + pl;
+  const int inner = heads * P, grp = h / (heads / groups);
+  if (slot == reserved_slot) {
+    for (int i = tid; i < n_new * PT; i += 256) {
+      const int j = i / PT, c = i - j * PT;
+      if (p0 + c < P) y[(int64_t)(t0 + j) * y_stride + h * P + p0 + c] = 0.f;
+    }
+    return;
+  }
+  float S[kNPT];
+  float* srow = state + (((int64_t)slot * heads + h) * P + p) * N + s * kNPT;
+#pragma unroll
+  for (int i = 0; i < kNPT; ++i) S[i] = (start > 0 && p < P && s * kNPT + i < N) ? srow[i] : 0.f;
+  const float a = expf(A_log[h]), dsk = Dp[h], bias = dt_bias[h];
+  for (int c0 = 0; c0 < n_new; c0 += kScanTokens) {
+    const int nt = min(kScanTokens, n_new - c0);
+    __syncthreads();   // the previous pass's ys / inputs are no longer read
+    for (int i = tid; i < nt * NL; i += 256) {
+      const int j = i / NL, r = i - j * NL, sl = r / (kNPT + 1), k = r - sl * (kNPT + 1), n = sl * kNPT + k;
+      const bool in = k < kNPT && n < N;
+      const float* row = xbc + (int64_t)(t0 + c0 + j) * x_stride + inner + grp * N;
+      Bs[i] = in ? row[n] : 0.f;
+      Cs[i] = in ? row[(int64_t)groups * N + n] : 0.f;
+    }
+    for (int i = tid; i < nt * PT; i += 256) {
+      const int j = i / PT, c = i - j * PT;
+      xs[i] = p0 + c < P ? xbc[(int64_t)(t0 + c0 + j) * x_stride + h * P + p0 + c] : 0.f;
+    }
+    if (tid < nt) {
+      const float dt = softplus_f(to_f<T>(proj[(int64_t)(t0 + c0 + tid) * p_stride + dt_off + h]) + bias);
+      dts[tid] = dt;
+      dAs[tid] = expf(-a * dt);
+    }
+    __syncthreads();
+    for (int j = 0; j < nt; ++j) {
+      const float dA = dAs[j], xv = xs[j * PT + pl], dx = dts[j] * xv;
+      const float* Br = Bs + j * NL + s * (kNPT + 1);
+      const float* Cr = Cs + j * NL + s * (kNPT + 1);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < kNPT; ++i) {
+        S[i] = fmaf(dA, S[i], dx * Br[i]);
+        acc = fmaf(S[i], Cr[i], acc);
+      }
+      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (s == 0) ys[j * PT + pl] = acc + dsk * xv;
+    }
+    __syncthreads();
+    for (int i = tid; i < nt * PT; i += 256) {
+      const int j = i / PT, c = i - j * PT;
+      if (p0 + c < P) y[(int64_t)(t0 + c0 + j) * y_stride + h * P + p0 + c] = ys[i];
+    }
+  }
+  if (p < P) {
+#pragma unroll
+    for (int i = 0; i < kNPT; ++i)
+      if (s * kNPT + i < N) srow[i] = S[i];
+  }
+}
+
+// grid (T, parts), 128 threads.  out[t, c] = v / sqrt(mean_part(v^2) + eps) * w[c], v = y[t, c] * silu(z[t, c]).
+template <typename T>
+__global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __restrict__ y, int64_t y_stride,
+                                                               const T* __restrict__ z, int64_t z_stride,
+                                                               const float* __restrict__ w, float eps,
+                                                               T* __restrict__ out, int64_t o_stride, int part) {
+  extern __shared__ float vals[];
+  __shared__ float red[4];
+  const int64_t t = blockIdx.x;
+  const int c0 = blockIdx.y * part;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < part; i += 128) {
+    const float v = y[t * y_stride + c0 + i] * silu_f(to_f<T>(z[t * z_stride + c0 + i]));
+    vals[i] = v;
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)part + eps);
+  for (int i = threadIdx.x; i < part; i += 128) out[t * o_stride + c0 + i] = from_f<T>(vals[i] * inv * w[c0 + i]);
+}
+
+int scan_slices(int N) {
+  int ns = 1;
+  while (ns * kNPT < N) ns <<= 1;
+  return ns;
+}
+
+}  // namespace
+}  // namespace cvllm
+
+using namespace cvllm;
+
+static int ssm_dtype_ok(int dtype) { return dtype == CVLLM_BF16 || dtype == CVLLM_F32; }
+
+extern "C" int cvllm_causal_conv(const void* proj, int64_t proj_stride, int x_off, int channels, int taps,
+                                 const float* weight, const float* bias, const void* conv_state,
+                                 const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                                 const int32_t* batch_mapping, int B, int max_new, float* out, int64_t out_stride,
+                                 int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && max_new >= 0 && channels > 0 && taps >= 1);
+  if (B == 0 || max_new == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(proj && weight && out && batch_mapping && ssm_dtype_ok(dtype) && (taps == 1 || conv_state));
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
+  CVLLM_CHECK_SUPPORTED(taps <= kMaxTaps && B <= 65535 && cdiv(channels, 128) <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
+  const dim3 grid(cdiv(max_new, kConvTokens), B, cdiv(channels, 128));
+  if (dtype == CVLLM_BF16)
+    causal_conv_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(proj), proj_stride, x_off,
+                                                            channels, taps, weight, bias,
+                                                            static_cast<const __nv_bfloat16*>(conv_state), g, out,
+                                                            out_stride);
+  else
+    causal_conv_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(proj), proj_stride, x_off, channels, taps,
+                                                    weight, bias, static_cast<const float*>(conv_state), g, out,
+                                                    out_stride);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_conv_state_update(const void* proj, int64_t proj_stride, int x_off, int channels, int taps,
+                                       void* conv_state, const int32_t* cu_seqlens_q, const int32_t* seq_start,
+                                       const int32_t* positions, const int32_t* batch_mapping, int B,
+                                       int reserved_slot, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && channels > 0 && taps >= 1);
+  if (B == 0 || taps == 1) return CVLLM_OK;
+  CVLLM_CHECK_ARG(proj && conv_state && batch_mapping && ssm_dtype_ok(dtype));
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : positions != nullptr);
+  CVLLM_CHECK_SUPPORTED(taps <= kMaxTaps && cdiv(channels, 128) <= 65535);
+  auto st = static_cast<cudaStream_t>(stream);
+  const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
+  const dim3 grid(B, cdiv(channels, 128));
+  if (dtype == CVLLM_BF16)
+    conv_state_update_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(proj), proj_stride,
+                                                                  x_off, channels, taps,
+                                                                  static_cast<__nv_bfloat16*>(conv_state), g,
+                                                                  reserved_slot);
+  else
+    conv_state_update_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(proj), proj_stride, x_off, channels,
+                                                          taps, static_cast<float*>(conv_state), g, reserved_slot);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* proj, int64_t proj_stride, int dt_off,
+                              const float* dt_bias, const float* A_log, const float* D, float* state,
+                              const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                              const int32_t* batch_mapping, int B, float* y, int64_t y_stride, int heads, int groups,
+                              int P, int N, int reserved_slot, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && P > 0 && N > 0);
+  if (B == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(xbc && proj && dt_bias && A_log && D && state && batch_mapping && y && ssm_dtype_ok(dtype));
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : positions != nullptr);
+  const int NS = scan_slices(N);
+  CVLLM_CHECK_SUPPORTED(NS <= 32 && B <= 65535);
+  const int PT = 256 / NS;
+  auto st = static_cast<cudaStream_t>(stream);
+  const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
+  const dim3 grid(heads, B, cdiv(P, PT));
+  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NS * (kNPT + 1) + 2 * kScanTokens * PT + 2 * kScanTokens);
+  static std::atomic<uint64_t> mask_b{0}, mask_f{0};
+  if (dtype == CVLLM_BF16) {
+    auto kern = ssm_scan_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, mask_b));
+    kern<<<grid, 256, smem, st>>>(xbc, xbc_stride, static_cast<const __nv_bfloat16*>(proj), proj_stride, dt_off, dt_bias,
+                                  A_log, D, state, g, y, y_stride, heads, groups, P, N, NS, reserved_slot);
+  } else {
+    auto kern = ssm_scan_kernel<float>;
+    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, mask_f));
+    kern<<<grid, 256, smem, st>>>(xbc, xbc_stride, static_cast<const float*>(proj), proj_stride, dt_off, dt_bias, A_log,
+                                  D, state, g, y, y_stride, heads, groups, P, N, NS, reserved_slot);
+  }
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}
+
+extern "C" int cvllm_gated_group_norm(const float* y, int64_t y_stride, const void* z, int64_t z_stride,
+                                      const float* weight, float eps, void* out, int64_t out_stride, int64_t rows,
+                                      int width, int parts, int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(rows >= 0 && width > 0 && parts > 0 && width % parts == 0);
+  if (rows == 0) return CVLLM_OK;
+  CVLLM_CHECK_ARG(y && z && weight && out && ssm_dtype_ok(dtype));
+  const int part = width / parts;
+  const size_t smem = (size_t)part * sizeof(float);
+  CVLLM_CHECK_SUPPORTED(smem <= 48 * 1024 && parts <= 65535 && rows <= 2147483647);
+  auto st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((unsigned)rows, parts);
+  if (dtype == CVLLM_BF16)
+    gated_group_norm_kernel<__nv_bfloat16><<<grid, 128, smem, st>>>(y, y_stride, static_cast<const __nv_bfloat16*>(z),
+                                                                    z_stride, weight, eps,
+                                                                    static_cast<__nv_bfloat16*>(out), out_stride, part);
+  else
+    gated_group_norm_kernel<float><<<grid, 128, smem, st>>>(y, y_stride, static_cast<const float*>(z), z_stride, weight,
+                                                            eps, static_cast<float*>(out), out_stride, part);
+  CVLLM_CHECK_LAUNCH();
+  return CVLLM_OK;
+}

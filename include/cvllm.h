@@ -404,38 +404,45 @@ int cvllm_selftest_umma(const void* a, const void* b, float* d, int mode,
  * --------------------------------------------------------------------- */
 
 /* Sandwich RMS norm, one launch per residual update, rows independent:
- *   y != NULL:      resid += y / sqrt(mean(y^2) + eps) * w_post        (y [rows, width] of y_dtype)
- *   w_pre != NULL:  out = resid / sqrt(mean(resid^2) + eps) * w_pre     (out [rows, width] of out_dtype)
- * y and w_post come together, w_pre and out come together.  width <= 12288.  Strides in elements. */
+ *   y != NULL:      resid += y / sqrt(mean(y^2) + eps) * (w_post + gain_offset)   (y [rows, width] of y_dtype;
+ *                   with `assign` the sum is replaced: resid = normed y)
+ *   w_pre != NULL:  out = resid / sqrt(mean(resid^2) + eps) * (w_pre + gain_offset)   (out [rows, width] of out_dtype)
+ *   out != NULL without w_pre:  out = resid rounded to out_dtype
+ * gain_offset 1 serves gains stored around zero.  y and w_post come together.  width <= 12288.  Strides in elements. */
 int cvllm_sandwich_norm(const void* y, int64_t y_stride, int y_dtype, const float* w_post, float* resid,
                         int64_t r_stride, const float* w_pre, void* out, int64_t o_stride, int out_dtype,
-                        int rows, int width, float eps, cvllm_stream_t stream);
+                        int rows, int width, float eps, float gain_offset, int assign, cvllm_stream_t stream);
 
-/* out[t, f] = act(x[t, f]) * x[t, F + f] for packed [gate | up] rows; kind 0 = silu, 1 = gelu (tanh form). */
+/* Packed [gate | up] rows -> out[t, f]; kind 0: silu(gate) * up, 1: gelu_tanh(gate) * up, 2: the clamped gated unit
+ * g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1).  limit is read by kind 2 only. */
 int cvllm_gated_act(const void* x, int64_t x_stride, void* out, int64_t o_stride, int64_t rows, int F, int kind,
-                    int dtype, cvllm_stream_t stream);
+                    float limit, int dtype, cvllm_stream_t stream);
 
 /* Router: s = softmax(logits[t, :E]); choice = s + correction (NULL = none).  The E outputs form `groups` equal
  * runs of neighbours; only the `keep` groups with the largest maximum of choice stay eligible; of those the `top`
  * largest choices are taken (ties: the lower index).  idx int32 [T, top], wts fp32 [T, top] = the plain s of the
- * chosen outputs, not renormalised.  E <= 2048, E % groups == 0, keep * E / groups >= top. */
+ * chosen outputs, not renormalised.  E <= 2048, E % groups == 0, keep * E / groups >= top.
+ * mode 1 (groups 1, no correction, top <= 32): the `top` largest LOGITS are taken and wts is the softmax over the
+ * chosen logits alone. */
 int cvllm_moe_route(const float* logits, int64_t l_stride, const float* correction, int T, int E, int top,
-                    int groups, int keep, int32_t* idx, float* wts, cvllm_stream_t stream);
+                    int groups, int keep, int mode, int32_t* idx, float* wts, cvllm_stream_t stream);
 
-/* out[t, :] = sum_r wts[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :]) + shared[t, :]
+/* out[t, :] = sum_r wts[t, r] * (idx[t, r] < n_real ? y[pos[t * top + r], :] : h[t, :]) + s_t * shared[t, :]
  * in fp32.  y holds one row per (token, choice) pair with a real expert, at the row pos gives (NULL: the pair's
- * own index); outputs idx >= n_real are identity experts (their output is the input h).  shared may be NULL. */
+ * own index); outputs idx >= n_real are identity experts (their output is the input h).  shared may be NULL.
+ * s_t = sigmoid(shared_gate[t * gate_stride]) (one fp32 logit per token), or 1 when shared_gate is NULL. */
 int cvllm_moe_combine(const void* y, const int32_t* pos, const float* wts, int top, const int32_t* idx, int n_real,
-                      const void* h, const void* shared, float* out, int64_t rows, int width, int dtype,
-                      cvllm_stream_t stream);
+                      const void* h, const void* shared, const float* shared_gate, int64_t gate_stride, float* out,
+                      int64_t rows, int width, int dtype, cvllm_stream_t stream);
 
 /* Expert products for a few tokens without host knowledge of the routing (decode, CUDA graphs): one row per
  * (token, choice) pair p with expert e = idx[p] and input row p / x_div of xs [.., K]:
  *   gated_kind 0 | 1:  out[p, f] = act(w[e, f, :] . x) * w[e, N + f, :] . x,  w [E, 2N, K], act = silu | gelu (tanh)
+ *   gated_kind 2:      the clamped gated unit of cvllm_gated_act on the same two products (limit)
  *   gated_kind -1:     out[p, n] = w[e, n, :] . x,                            w [E, N, K]
  * Pairs with e >= n_real are left untouched.  out [pairs, N]. */
 int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const int32_t* idx, int n_real, void* out,
-                      int pairs, int N, int K, int gated_kind, int dtype, cvllm_stream_t stream);
+                      int pairs, int N, int K, int gated_kind, float limit, int dtype, cvllm_stream_t stream);
 
 /* ------------------------------------------------------------------------
  * Biased attention over the paged cache (csrc/bias_attn.cu): any head size, CVLLM_BF16 or CVLLM_F32 storage,
@@ -443,7 +450,8 @@ int cvllm_expert_gemv(const void* xs, int x_div, const void* w, const int32_t* i
  * floor(i / chunk) == floor(j / chunk) (chunk 0: no chunking; slopes NULL: no bias);
  * p_j = exp(s_j) / (sink + sum exp(s_j)), sink 0 or 1.  Positions count from the start of each sequence.
  * The cache is the one of the store path: k_cache [rows, D], v_cache [rows, Dv], page_table[slot, head, page]
- * with the two strides given, page_size rows per page.
+ * with the two strides given, page_size rows per page.  v_stride (elements between value rows; 0 = Dv) lets the
+ * values be a column range of wider rows, e.g. v_cache = k_cache with v_stride = D: the first Dv columns of the keys.
  * --------------------------------------------------------------------- */
 
 /* qkv [T, H*D + G*D + G*Dv] packed rows -> q_out [T, H, D] (per-head RMS norm, weight q_weight [D] or NULL),
@@ -466,7 +474,7 @@ int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cac
                            const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* batch_mapping,
                            const float* slopes, int chunk, int sink, float scale, void* out, int B, int max_new,
                            int H, int G, int D, int Dv, int total_tokens, int64_t cache_rows, int pages_per_head,
-                           int dtype, cvllm_stream_t stream);
+                           int64_t v_stride, int dtype, cvllm_stream_t stream);
 
 /* Decode: one query per sequence at position positions[b] (its key is in the cache already).  q [B, H, D],
  * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 256.  With D and Dv multiples of 8 (and D <= 256) the keys
@@ -476,7 +484,66 @@ int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cac
                            int64_t table_stride_slot, int64_t table_stride_head, int page_size,
                            const int32_t* positions, const int32_t* batch_mapping, const float* slopes, int chunk,
                            int sink, float scale, void* out, int B, int H, int G, int D, int Dv, int reserved_slot,
-                           int splits, float* workspace, size_t workspace_bytes, int dtype, cvllm_stream_t stream);
+                           int splits, float* workspace, size_t workspace_bytes, int64_t v_stride, int dtype,
+                           cvllm_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * Latent attention (csrc/latent_attn.cu): the steps around attention in the latent space.  The cache row of a token
+ * is [c | k_rot] (kv_rank + rot_dim numbers, one key/value head).  inv_freq: rot_dim / 2 doubles, base ** (-2 i / rot_dim).
+ * --------------------------------------------------------------------- */
+
+/* proj [T, ..] rows hold the query latent at q_off (q_rank numbers) and - kv_off >= 0 - the kv latent followed by the
+ * shared key part at kv_off (kv_rank + rot_dim).  cq_out [T, q_rank] = RMS norm(query latent) * q_weight;
+ * cache row of (token_slot[t], positions[t]) = [RMS norm(kv latent) * kv_weight | rotate(shared key part)];
+ * lens[slot] (may be NULL) is raised to positions[t] + 1.  page_table[slot * table_stride_slot + page].
+ * Tokens of reserved_slot store nothing. */
+int cvllm_latent_norm_store(const void* proj, int64_t proj_stride, int q_off, int q_rank, int kv_off, int kv_rank,
+                            int rot_dim, const float* q_weight, const float* kv_weight, float eps,
+                            const double* inv_freq, const int32_t* positions, const int32_t* token_slot, void* cq_out,
+                            void* cache, const int32_t* page_table, int64_t table_stride_slot, int page_size,
+                            int32_t* lens, int T, int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* q [T, H, D + rot_dim] (row stride q_stride): q_full[t * full_stride + h * full_head + off + 0 .. rot_dim) =
+ * rotate(q[t, h, D .. D + rot_dim)) at positions[t]. */
+int cvllm_latent_q_rope(const void* q, int64_t q_stride, int H, int D, int rot_dim, const double* inv_freq,
+                        const int32_t* positions, void* q_full, int64_t full_stride, int full_head, int off, int T,
+                        int dtype, cvllm_stream_t stream);
+
+/* out[t, c] = x[t, c] * sigmoid(gate[t, c]) */
+int cvllm_sigmoid_gate(const void* x, int64_t x_stride, const void* gate, int64_t g_stride, void* out,
+                       int64_t o_stride, int64_t rows, int width, int dtype, cvllm_stream_t stream);
+
+/* ------------------------------------------------------------------------
+ * State-space mixer (csrc/ssm.cu).  A step brings sequence b the tokens cu_seqlens_q[b] .. cu_seqlens_q[b + 1] - 1 at
+ * positions seq_start[b] + 0, 1, ..; cu_seqlens_q NULL = one token per sequence at positions[b].  batch_mapping[b] is
+ * the sequence's slot of the state pool.  A portion that starts at position 0 starts from a zero state.
+ * --------------------------------------------------------------------- */
+
+/* out[t, ch] (fp32) = silu(bias[ch] + sum_k weight[ch, k] * x(t - (taps - 1 - k), ch)) with x = columns x_off.. of proj;
+ * inputs before the portion come from conv_state [slots, taps - 1, channels] (zeros before position 0). taps <= 16. */
+int cvllm_causal_conv(const void* proj, int64_t proj_stride, int x_off, int channels, int taps, const float* weight,
+                      const float* bias, const void* conv_state, const int32_t* cu_seqlens_q,
+                      const int32_t* seq_start, const int32_t* positions, const int32_t* batch_mapping, int B,
+                      int max_new, float* out, int64_t out_stride, int dtype, cvllm_stream_t stream);
+
+/* conv_state of every sequence of the step := its last taps - 1 inputs (after cvllm_causal_conv has read the old one). */
+int cvllm_conv_state_update(const void* proj, int64_t proj_stride, int x_off, int channels, int taps, void* conv_state,
+                            const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                            const int32_t* batch_mapping, int B, int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* xbc [T, heads * P + 2 * groups * N] fp32 = (x | B | C) after the convolution; dt_raw = proj[t, dt_off + h];
+ * state [slots, heads, P, N] fp32, read (portions that start after position 0) and written in place;
+ * y [T, heads * P] fp32 = S_t C_t + D_h x_t.  N <= 512. */
+int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* proj, int64_t proj_stride, int dt_off,
+                   const float* dt_bias, const float* A_log, const float* D, float* state,
+                   const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
+                   const int32_t* batch_mapping, int B, float* y, int64_t y_stride, int heads, int groups, int P, int N,
+                   int reserved_slot, int dtype, cvllm_stream_t stream);
+
+/* out[t, c] = v / sqrt(mean over c's part of v^2 + eps) * weight[c], v = y[t, c] * silu(z[t, c]); `parts` equal parts. */
+int cvllm_gated_group_norm(const float* y, int64_t y_stride, const void* z, int64_t z_stride, const float* weight,
+                           float eps, void* out, int64_t out_stride, int64_t rows, int width, int parts, int dtype,
+                           cvllm_stream_t stream);
 
 #ifdef __cplusplus
 }
