@@ -225,3 +225,6 @@ class BatasunForCausalLM(nn.Module):
             else:
                 val = val * (p.shape[-1] ** -0.5)
             p.copy_(val.to(p.dtype))
+        for layer in self.layers:      # the shared expert's gate logit (the router's extra row) has no bias
+            if layer.mlp is not None and layer.mlp.router_bias is not None:
+                layer.mlp.router_bias[layer.mlp.total:].zero_()

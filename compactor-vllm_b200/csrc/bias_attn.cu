@@ -481,7 +481,7 @@ int launch_varlen_mma(const void* q, const PagedKV& c, const int32_t* cu_q, cons
 // states are merged through shared memory.
 // ---------------------------------------------------------------------------------------------------------
 constexpr int kDecWarps = 4;
-constexpr int kDecCols = 8;  // output columns per lane: Dv <= 256
+constexpr int kDecCols = 16;  // output columns per lane: Dv <= 512
 
 template <typename T>
 __global__ void __launch_bounds__(kDecWarps * 32) bias_attn_decode_kernel(
@@ -973,7 +973,8 @@ int dispatch_dvc(int dvc, const void* q, const PagedKV& c, const int32_t* cu_q, 
   if (dvc <= 4) CVLLM_GO(4);
   if (dvc <= 6) CVLLM_GO(6);
   if (dvc <= 8) CVLLM_GO(8);
-  CVLLM_GO(16);
+  if (dvc <= 16) CVLLM_GO(16);
+  CVLLM_GO(32);
 #undef CVLLM_GO
 }
 
@@ -1048,7 +1049,7 @@ extern "C" int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const 
   if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(q && k_cache && v_cache && page_table && cu_seqlens_q && seq_start && batch_mapping && out &&
                   check_dtype(dtype) && page_size > 0);
-  CVLLM_CHECK_SUPPORTED(Dv <= 256 && B <= 65535 && H <= 65535);
+  CVLLM_CHECK_SUPPORTED(Dv <= 512 && B <= 65535 && H <= 65535);
   CVLLM_CHECK_ARG(v_stride == 0 || v_stride >= Dv);
   if (v_stride == 0) v_stride = Dv;
   auto st = static_cast<cudaStream_t>(stream);

@@ -466,7 +466,7 @@ int cvllm_qknorm_store(const void* qkv, int64_t qkv_stride, const float* q_weigh
 /* Portions: sequence b brings tokens cu_seqlens_q[b] .. cu_seqlens_q[b+1]-1 at positions seq_start[b] + 0, 1, ...;
  * all their keys (and every earlier one) are in the cache of slot batch_mapping[b].  out [T, H, Dv].
  * max_new = the largest number of new tokens of one sequence, total_tokens = T, cache_rows = rows of k_cache,
- * pages_per_head = the page table's last dimension.  Dv <= 256.
+ * pages_per_head = the page table's last dimension.  Dv <= 512.
  * Kernels: tcgen05 / TMEM / TMA (bfloat16, D = Dv = 128, page_size % 128 == 0, H / G even, dense page table);
  * mma.sync (bfloat16, D % 16 == 0, Dv % 8 == 0, both <= 128); fp32 FMA (everything else, float32 included). */
 int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
@@ -477,7 +477,7 @@ int cvllm_bias_attn_varlen(const void* q, const void* k_cache, const void* v_cac
                            int64_t v_stride, int dtype, cvllm_stream_t stream);
 
 /* Decode: one query per sequence at position positions[b] (its key is in the cache already).  q [B, H, D],
- * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 256.  With D and Dv multiples of 8 (and D <= 256) the keys
+ * out [B, H, Dv]; rows of reserved_slot give zeros.  Dv <= 512.  With D and Dv multiples of 8 (and D <= 256) the keys
  * of a sequence are cut into `splits` parts that run on CTAs of their own; splits > 1 needs a workspace of
  * 4 * B * H * splits * (2 + Dv) bytes.  Other sizes run one CTA per (sequence, head) and ignore `splits`. */
 int cvllm_bias_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int32_t* page_table,
