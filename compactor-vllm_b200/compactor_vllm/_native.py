@@ -88,8 +88,9 @@ _SIGNATURES = {
     "cvllm_sigmoid_gate": (_i, [_p, _i64, _p, _i64, _p, _i64, _i64, _i, _i, _p]),
     "cvllm_causal_conv": (_i, [_p, _i64, _i, _i, _i, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i64, _i, _p]),
     "cvllm_conv_state_update": (_i, [_p, _i64, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _i, _p]),
-    "cvllm_ssm_scan": (_i, [_p, _i64, _p, _i64, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _i64, _i, _i, _i, _i,
-                            _i, _i, _p]),
+    "cvllm_ssm_scan_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "cvllm_ssm_scan": (_i, [_p, _i64, _p, _i64, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _i64, _i, _i, _i, _i,
+                            _i, _p, _sz, _i, _p]),
     "cvllm_gated_group_norm": (_i, [_p, _i64, _p, _i64, _p, _f, _p, _i64, _i64, _i, _i, _i, _p]),
     "cvllm_qknorm_store": (_i, [_p, _i64, _p, _p, _f, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _p,
                                 _i, _i, _i, _i, _i, _i, _i, _p]),

@@ -68,10 +68,12 @@ class StateSpaceMixer(nn.Module):
                                             N.ptr(self.conv_state), *geom, N.ptr(slots), B, RESERVED_BATCH, code, st),
                 "cvllm_conv_state_update")
         y = torch.empty((T, self.inner), dtype=torch.float32, device=dev)
+        ws_bytes = lib.cvllm_ssm_scan_workspace_bytes(B, max_new, self.heads, self.vdim, self.state)
+        ws = N.workspace(dev, ws_bytes, "ssm_scan") if ws_bytes else None     # long portions: per-segment states
         N.check(lib.cvllm_ssm_scan(N.ptr(xbc), xbc.stride(0), N.ptr(proj), proj.stride(0), self.inner + self.channels,
                                    N.ptr(self.dt_bias), N.ptr(self.A_log), N.ptr(self.D), N.ptr(self.ssm_state), *geom,
-                                   N.ptr(slots), B, N.ptr(y), y.stride(0), self.heads, self.groups, self.vdim, self.state,
-                                   RESERVED_BATCH, code, st), "cvllm_ssm_scan")
+                                   N.ptr(slots), B, max_new, N.ptr(y), y.stride(0), self.heads, self.groups, self.vdim,
+                                   self.state, RESERVED_BATCH, N.ptr(ws), ws_bytes, code, st), "cvllm_ssm_scan")
         out = torch.empty((T, self.inner), dtype=proj.dtype, device=dev)
         N.check(lib.cvllm_gated_group_norm(N.ptr(y), y.stride(0), N.ptr(proj), proj.stride(0), N.ptr(self.norm_weight),
                                            self.eps, N.ptr(out), out.stride(0), T, self.inner, self.norm_groups, code, st),

@@ -127,9 +127,15 @@ __global__ void __launch_bounds__(128) conv_state_update_kernel(const T* __restr
 constexpr int kScanTokens = 16;   // tokens staged per pass
 constexpr int kNPT = 16;          // state channels per thread
 
-// grid (heads, B, value tiles), 256 threads = PT value channels x NS slices of the state dimension (NS a power of two,
-// NS * 16 >= N, PT = 256 / NS).  Thread (p, s) keeps S[p, 16 s .. 16 s + 15] in registers over the whole portion.
+// grid (heads, B * nseg, value tiles), 256 threads = PT value channels x NS slices of the state dimension (NS a power
+// of two, NS * 16 >= N, PT = 256 / NS).  Thread (p, s) keeps S[p, 16 s .. 16 s + 15] in registers over its tokens.
 // xbc [T, inner + 2 G N] fp32 = conv output (x | B | C); dt_raw = column dt_off + h of proj.
+// A portion is cut into nseg segments of seg tokens (nseg 1: the whole portion).  mode 0: the CTA runs the whole
+// portion from the pool's state.  Long portions run in three launches so that the segments of one sequence run side by
+// side: mode 1 runs every segment but a sequence's last from a ZERO state, without output, and leaves the segment's
+// end state and its summed step sizes in seg_state / seg_dt; ssm_seg_combine_kernel turns those into each segment's true
+// initial state (S_init[k + 1] = exp(-a sum_dt[k]) S_init[k] + S_local[k], the recurrence being linear in S);
+// mode 2 reruns every segment from its initial state with output, and a sequence's last segment writes the pool.
 template <typename T>
 __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__ xbc, int64_t x_stride,
                                                        const T* __restrict__ proj, int64_t p_stride, int dt_off,
@@ -137,7 +143,8 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
                                                        const float* __restrict__ A_log, const float* __restrict__ Dp,
                                                        float* __restrict__ state, StepGeom g, float* __restrict__ y,
                                                        int64_t y_stride, int heads, int groups, int P, int N, int NS,
-                                                       int reserved_slot) {
+                                                       int reserved_slot, int mode, int nseg, int seg,
+                                                       float* __restrict__ seg_state, float* __restrict__ seg_dt) {
   extern __shared__ float sm[];
   const int PT = 256 / NS;
   const int NL = NS * (kNPT + 1);               // padded row of B / C: slice s starts at s * 17
@@ -147,31 +154,39 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
   float* ys = xs + kScanTokens * PT;            // [kScanTokens][PT]
   float* dts = ys + kScanTokens * PT;           // [kScanTokens]
   float* dAs = dts + kScanTokens;               // [kScanTokens]
-  const int h = blockIdx.x, b = blockIdx.y, p0 = blockIdx.z * PT;
+  const int h = blockIdx.x, b = blockIdx.y / nseg, k = blockIdx.y - b * nseg, p0 = blockIdx.z * PT;
   int t0, n_new, start;
   portion(g, b, t0, n_new, start);
-  if (n_new <= 0) return;
+  const int j_begin = mode == 0 ? 0 : k * seg;
+  const int j_end = mode == 0 ? n_new : min(n_new, j_begin + seg);
+  if (j_begin >= j_end) return;
+  const bool last_seg = j_end == n_new;
+  if (mode == 1 && last_seg) return;            // nobody needs the end state of a sequence's last segment early
   const int slot = g.slots[b];
   const int tid = threadIdx.x, s = tid & (NS - 1), pl = tid / NS, p = p0 + pl;
   const int inner = heads * P, grp = h / (heads / groups);
   if (slot == reserved_slot) {
-    for (int i = tid; i < n_new * PT; i += 256) {
+    if (mode == 1) return;
+    for (int i = tid; i < (j_end - j_begin) * PT; i += 256) {
       const int j = i / PT, c = i - j * PT;
-      if (p0 + c < P) y[(int64_t)(t0 + j) * y_stride + h * P + p0 + c] = 0.f;
+      if (p0 + c < P) y[(int64_t)(t0 + j_begin + j) * y_stride + h * P + p0 + c] = 0.f;
     }
     return;
   }
   float S[kNPT];
-  float* srow = state + (((int64_t)slot * heads + h) * P + p) * N + s * kNPT;
+  float* pool_row = state + (((int64_t)slot * heads + h) * P + p) * N + s * kNPT;
+  float* seg_row = seg_state ? seg_state + ((((int64_t)b * nseg + k) * heads + h) * P + p) * N + s * kNPT : nullptr;
+  const float* init = mode == 2 ? seg_row : ((mode == 0 && start > 0) ? pool_row : nullptr);
 #pragma unroll
-  for (int i = 0; i < kNPT; ++i) S[i] = (start > 0 && p < P && s * kNPT + i < N) ? srow[i] : 0.f;
+  for (int i = 0; i < kNPT; ++i) S[i] = (init && p < P && s * kNPT + i < N) ? init[i] : 0.f;
   const float a = expf(A_log[h]), dsk = Dp[h], bias = dt_bias[h];
-  for (int c0 = 0; c0 < n_new; c0 += kScanTokens) {
-    const int nt = min(kScanTokens, n_new - c0);
+  float dt_sum = 0.f;
+  for (int c0 = j_begin; c0 < j_end; c0 += kScanTokens) {
+    const int nt = min(kScanTokens, j_end - c0);
     __syncthreads();   // the previous pass's ys / inputs are no longer read
     for (int i = tid; i < nt * NL; i += 256) {
-      const int j = i / NL, r = i - j * NL, sl = r / (kNPT + 1), k = r - sl * (kNPT + 1), n = sl * kNPT + k;
-      const bool in = k < kNPT && n < N;
+      const int j = i / NL, r = i - j * NL, sl = r / (kNPT + 1), kk = r - sl * (kNPT + 1), n = sl * kNPT + kk;
+      const bool in = kk < kNPT && n < N;
       const float* row = xbc + (int64_t)(t0 + c0 + j) * x_stride + inner + grp * N;
       Bs[i] = in ? row[n] : 0.f;
       Cs[i] = in ? row[(int64_t)groups * N + n] : 0.f;
@@ -189,6 +204,12 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
     for (int j = 0; j < nt; ++j) {
       const float dA = dAs[j], xv = xs[j * PT + pl], dx = dts[j] * xv;
       const float* Br = Bs + j * NL + s * (kNPT + 1);
+      dt_sum += dts[j];
+      if (mode == 1) {
+#pragma unroll
+        for (int i = 0; i < kNPT; ++i) S[i] = fmaf(dA, S[i], dx * Br[i]);
+        continue;
+      }
       const float* Cr = Cs + j * NL + s * (kNPT + 1);
       float acc = 0.f;
 #pragma unroll
@@ -199,16 +220,45 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
       for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (s == 0) ys[j * PT + pl] = acc + dsk * xv;
     }
+    if (mode == 1) continue;
     __syncthreads();
     for (int i = tid; i < nt * PT; i += 256) {
       const int j = i / PT, c = i - j * PT;
       if (p0 + c < P) y[(int64_t)(t0 + c0 + j) * y_stride + h * P + p0 + c] = ys[i];
     }
   }
-  if (p < P) {
+  float* dst = mode == 1 ? seg_row : ((mode == 0 || last_seg) ? pool_row : nullptr);
+  if (dst && p < P) {
 #pragma unroll
     for (int i = 0; i < kNPT; ++i)
-      if (s * kNPT + i < N) srow[i] = S[i];
+      if (s * kNPT + i < N) dst[i] = S[i];
+  }
+  if (mode == 1 && tid == 0 && blockIdx.z == 0) seg_dt[((int64_t)b * nseg + k) * heads + h] = dt_sum;
+}
+
+// grid (heads, B), 256 threads over the P * N state entries of a head: seg_state[b, k] (the segment's local end state,
+// from a zero start) becomes the segment's initial state, k = 0 .. the sequence's segment count - 1.
+__global__ void __launch_bounds__(256) ssm_seg_combine_kernel(float* __restrict__ seg_state,
+                                                              const float* __restrict__ seg_dt,
+                                                              const float* __restrict__ state,
+                                                              const float* __restrict__ A_log, StepGeom g, int heads,
+                                                              int P, int N, int nseg, int seg, int reserved_slot) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  int t0, n_new, start;
+  portion(g, b, t0, n_new, start);
+  const int slot = g.slots[b];
+  if (slot == reserved_slot || n_new <= 0) return;
+  const int mine = (n_new + seg - 1) / seg;
+  const float a = expf(A_log[h]);
+  const int64_t per = (int64_t)P * N;
+  for (int e = threadIdx.x; e < per; e += 256) {
+    float cur = start > 0 ? state[((int64_t)slot * heads + h) * per + e] : 0.f;
+    for (int k = 0; k < mine; ++k) {
+      float* cell = seg_state + (((int64_t)b * nseg + k) * heads + h) * per + e;
+      const float local = k < mine - 1 ? *cell : 0.f;
+      *cell = cur;
+      if (k < mine - 1) cur = fmaf(expf(-a * seg_dt[((int64_t)b * nseg + k) * heads + h]), cur, local);
+    }
   }
 }
 
@@ -239,6 +289,15 @@ int scan_slices(int N) {
   int ns = 1;
   while (ns * kNPT < N) ns <<= 1;
   return ns;
+}
+
+// Tokens per segment of a step whose longest portion has max_new tokens; 0 = portions run whole, in one launch.
+// Segments are a multiple of the staging pass; the test option "ssm_segment" overrides the product's 256.
+int scan_segment(int max_new) {
+  int seg = test_options().ssm_segment.load();
+  if (seg <= 0) seg = 256;
+  seg = cdiv(seg, kScanTokens) * kScanTokens;
+  return max_new > seg ? seg : 0;
 }
 
 }  // namespace
@@ -298,35 +357,66 @@ extern "C" int cvllm_conv_state_update(const void* proj, int64_t proj_stride, in
   return CVLLM_OK;
 }
 
+extern "C" size_t cvllm_ssm_scan_workspace_bytes(int B, int max_new, int heads, int P, int N) {
+  const int seg = scan_segment(max_new);
+  if (seg <= 0) return 0;
+  const size_t nseg = (size_t)cdiv(max_new, seg);
+  return sizeof(float) * (size_t)B * nseg * heads * ((size_t)P * N + 1);
+}
+
 extern "C" int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* proj, int64_t proj_stride, int dt_off,
                               const float* dt_bias, const float* A_log, const float* D, float* state,
                               const int32_t* cu_seqlens_q, const int32_t* seq_start, const int32_t* positions,
-                              const int32_t* batch_mapping, int B, float* y, int64_t y_stride, int heads, int groups,
-                              int P, int N, int reserved_slot, int dtype, cvllm_stream_t stream) {
-  CVLLM_CHECK_ARG(B >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && P > 0 && N > 0);
-  if (B == 0) return CVLLM_OK;
+                              const int32_t* batch_mapping, int B, int max_new, float* y, int64_t y_stride, int heads,
+                              int groups, int P, int N, int reserved_slot, float* workspace, size_t workspace_bytes,
+                              int dtype, cvllm_stream_t stream) {
+  CVLLM_CHECK_ARG(B >= 0 && heads > 0 && groups > 0 && heads % groups == 0 && P > 0 && N > 0 && max_new >= 0);
+  if (B == 0 || max_new == 0) return CVLLM_OK;
   CVLLM_CHECK_ARG(xbc && proj && dt_bias && A_log && D && state && batch_mapping && y && ssm_dtype_ok(dtype));
-  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : positions != nullptr);
+  CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
   const int NS = scan_slices(N);
-  CVLLM_CHECK_SUPPORTED(NS <= 32 && B <= 65535);
+  CVLLM_CHECK_SUPPORTED(NS <= 32);
   const int PT = 256 / NS;
   auto st = static_cast<cudaStream_t>(stream);
   const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
-  const dim3 grid(heads, B, cdiv(P, PT));
+  const int seg = scan_segment(max_new);
+  const int nseg = seg > 0 ? cdiv(max_new, seg) : 1;
+  CVLLM_CHECK_SUPPORTED((int64_t)B * nseg <= 65535);
+  float* seg_state = nullptr;
+  float* seg_dt = nullptr;
+  if (seg > 0) {
+    if (!workspace || workspace_bytes < cvllm_ssm_scan_workspace_bytes(B, max_new, heads, P, N)) {
+      set_last_error("state-space scan workspace too small");
+      return CVLLM_E_WORKSPACE;
+    }
+    seg_state = workspace;
+    seg_dt = workspace + (size_t)B * nseg * heads * P * N;
+  }
+  const dim3 grid(heads, B * nseg, cdiv(P, PT));
   const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NS * (kNPT + 1) + 2 * kScanTokens * PT + 2 * kScanTokens);
   static std::atomic<uint64_t> mask_b{0}, mask_f{0};
-  if (dtype == CVLLM_BF16) {
-    auto kern = ssm_scan_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, mask_b));
-    kern<<<grid, 256, smem, st>>>(xbc, xbc_stride, static_cast<const __nv_bfloat16*>(proj), proj_stride, dt_off, dt_bias,
-                                  A_log, D, state, g, y, y_stride, heads, groups, P, N, NS, reserved_slot);
-  } else {
-    auto kern = ssm_scan_kernel<float>;
-    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, mask_f));
-    kern<<<grid, 256, smem, st>>>(xbc, xbc_stride, static_cast<const float*>(proj), proj_stride, dt_off, dt_bias, A_log,
-                                  D, state, g, y, y_stride, heads, groups, P, N, NS, reserved_slot);
+#define CVLLM_SCAN(T, MASK, MODE)                                                                                  \
+  do {                                                                                                             \
+    auto kern = ssm_scan_kernel<T>;                                                                                \
+    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, MASK)); \
+    kern<<<grid, 256, smem, st>>>(xbc, xbc_stride, static_cast<const T*>(proj), proj_stride, dt_off, dt_bias, A_log, D, \
+                                  state, g, y, y_stride, heads, groups, P, N, NS, reserved_slot, MODE, nseg,      \
+                                  seg > 0 ? seg : max_new, seg_state, seg_dt);                                     \
+    CVLLM_CHECK_LAUNCH();                                                                                          \
+  } while (0)
+  if (seg <= 0) {
+    if (dtype == CVLLM_BF16) CVLLM_SCAN(__nv_bfloat16, mask_b, 0);
+    else CVLLM_SCAN(float, mask_f, 0);
+    return CVLLM_OK;
   }
+  if (dtype == CVLLM_BF16) CVLLM_SCAN(__nv_bfloat16, mask_b, 1);
+  else CVLLM_SCAN(float, mask_f, 1);
+  ssm_seg_combine_kernel<<<dim3(heads, B), 256, 0, st>>>(seg_state, seg_dt, state, A_log, g, heads, P, N, nseg, seg,
+                                                         reserved_slot);
   CVLLM_CHECK_LAUNCH();
+  if (dtype == CVLLM_BF16) CVLLM_SCAN(__nv_bfloat16, mask_b, 2);
+  else CVLLM_SCAN(float, mask_f, 2);
+#undef CVLLM_SCAN
   return CVLLM_OK;
 }
 

@@ -435,6 +435,39 @@ def test_state_far_back_reaches_the_last_token():
         assert rel_err(run_in_portions(r, toks, sizes), want) < TOL["float32"], sizes
 
 
+@pytest.mark.parametrize("seg", [16, 32, 48])
+def test_long_portions_run_in_segments(seg):
+    """Portions longer than a segment run their segments side by side (local states, a combine pass, a rerun); with short
+    segments every cut of the test falls somewhere else: on a segment's edge, one token past it, inside it, and a batch
+    of a long portion beside short ones and beside a sequence that continues from a carried state."""
+    from compactor_vllm import _native as N
+    from oracle import batasun as O
+
+    N.set_test_option("ssm_segment", seg)
+    try:
+        r = make_runner(model_cfg([(mamba(3, 20, 33, 1, 3, 3), None), (mamba(4, 6, 10, 2, 4, 2), moe())]), "float32",
+                        pages=40, page_size=16)
+        om = oracle_model(r.model)
+        toks = tokens(150, 89, 23)
+        want = O.forward(om, toks)
+        for sizes in ([150], [seg + 1, 2 * seg, 5], [3, 2 * seg + 1, seg], [seg, seg, seg + 7]):
+            assert rel_err(run_in_portions(r, toks, sizes), want) < TOL["float32"], sizes
+        reqs = [tokens(n, 89, 50 + i) for i, n in enumerate((140, 5, 70))]
+        wants = [O.forward(om, t) for t in reqs]
+        seqs = [new_seq() for _ in reqs]
+        head = feed(r, seqs[2], reqs[2][:9])                       # request 2 carries a state into the big step
+        for s_, t in zip(seqs[:2], reqs[:2]):
+            s_.prompt_token_ids.extend(t)
+        seqs[2].prompt_token_ids.extend(reqs[2][9:])
+        logits = r.run_step([(seqs[0], reqs[0]), (seqs[1], reqs[1]), (seqs[2], reqs[2][9:])], rows=list(range(140 + 5 + 61)))
+        r.release(seqs)
+        assert rel_err(logits[:140], wants[0]) < TOL["float32"]
+        assert rel_err(logits[140:145], wants[1]) < TOL["float32"]
+        assert rel_err(torch.cat([head, logits[145:]]), wants[2]) < TOL["float32"]
+    finally:
+        N.set_test_option("ssm_segment", 0)
+
+
 # ---------------------------------------------------------------------------------- batches, pages and slots reused
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_mixed_batches_equal_each_request_alone(dtype):
