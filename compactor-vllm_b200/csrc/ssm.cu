@@ -95,6 +95,50 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const T* __restrict__ 
   }
 }
 
+// The same for a compile-time number of taps: a thread walks kConvRun tokens of its channel with the last TAPS - 1
+// inputs in registers, so every input is read once.  grid (token runs, B, channel tiles), 128 threads.
+constexpr int kConvRun = 32;
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128) causal_conv_run_kernel(const T* __restrict__ proj, int64_t p_stride, int x_off,
+                                                              int C, const float* __restrict__ w,
+                                                              const float* __restrict__ bias,
+                                                              const T* __restrict__ conv_state, StepGeom g,
+                                                              float* __restrict__ out, int64_t o_stride) {
+  const int b = blockIdx.y;
+  int t0, n_new, start;
+  portion(g, b, t0, n_new, start);
+  const int j0 = blockIdx.x * kConvRun;
+  if (j0 >= n_new) return;
+  const int ch = blockIdx.z * 128 + threadIdx.x;
+  if (ch >= C) return;
+  const int slot = g.slots[b];
+  float wk[TAPS], win[TAPS];          // win[k] = input at j - (TAPS - 1 - k); win[TAPS - 1] is the current token's
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) wk[k] = w[(int64_t)ch * TAPS + k];
+  const float bv = bias ? bias[ch] : 0.f;
+  const T* st = conv_state + (int64_t)slot * (TAPS - 1) * C + ch;
+  const T* in = proj + (int64_t)t0 * p_stride + x_off + ch;
+#pragma unroll
+  for (int k = 0; k < TAPS - 1; ++k) {
+    const int src = j0 - (TAPS - 1 - k);
+    float v = 0.f;
+    if (src >= 0) v = to_f<T>(in[(int64_t)src * p_stride]);
+    else if (start + src >= 0) v = to_f<T>(st[(int64_t)(TAPS - 1 + src) * C]);
+    win[k] = v;
+  }
+  const int j1 = min(j0 + kConvRun, n_new);
+  for (int j = j0; j < j1; ++j) {
+    win[TAPS - 1] = to_f<T>(in[(int64_t)j * p_stride]);
+    float acc = bv;
+#pragma unroll
+    for (int k = 0; k < TAPS; ++k) acc = fmaf(wk[k], win[k], acc);
+    out[(int64_t)(t0 + j) * o_stride + ch] = silu_f(acc);
+#pragma unroll
+    for (int k = 0; k < TAPS - 1; ++k) win[k] = win[k + 1];
+  }
+}
+
 // grid (B, channel tiles), 128 threads: a thread reads what it needs of its channel's old state, then writes the new.
 template <typename T>
 __global__ void __launch_bounds__(128) conv_state_update_kernel(const T* __restrict__ proj, int64_t p_stride,
@@ -125,36 +169,52 @@ __global__ void __launch_bounds__(128) conv_state_update_kernel(const T* __restr
 }
 
 constexpr int kScanTokens = 16;   // tokens staged per pass
-constexpr int kNPT = 16;          // state channels per thread
 
-// grid (heads, B * nseg, value tiles), 256 threads = PT value channels x NS slices of the state dimension (NS a power
-// of two, NS * 16 >= N, PT = 256 / NS).  Thread (p, s) keeps S[p, 16 s .. 16 s + 15] in registers over its tokens.
+constexpr int kPad = 4;           // floats between the 16-value slices of a staged B / C row (keeps 16-byte alignment)
+
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(addr), "l"(gmem) : "memory");
+}
+
+__device__ __forceinline__ void cp_async16(float* smem, const float* gmem) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem) : "memory");
+}
+
+__device__ __forceinline__ float f4_at(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// grid (heads, B * nseg, value tiles), PT * NS threads: NS slices of the state dimension (a power of two, NS * 16 >= N)
+// times PT value channels; thread (pl, s) keeps S[p, 16 s .. 16 s + 15] for its TWO value channels p = p0 + pl and
+// p0 + pl + PT in registers over its tokens, so that the 32 values of B_t and C_t it reads from shared memory per token
+// (eight 16-byte loads) serve 64 state updates.
 // xbc [T, inner + 2 G N] fp32 = conv output (x | B | C); dt_raw = column dt_off + h of proj.
 // A portion is cut into nseg segments of seg tokens (nseg 1: the whole portion).  mode 0: the CTA runs the whole
-// portion from the pool's state.  Long portions run in three launches so that the segments of one sequence run side by
-// side: mode 1 runs every segment but a sequence's last from a ZERO state, without output, and leaves the segment's
-// end state and its summed step sizes in seg_state / seg_dt; ssm_seg_combine_kernel turns those into each segment's true
-// initial state (S_init[k + 1] = exp(-a sum_dt[k]) S_init[k] + S_local[k], the recurrence being linear in S);
-// mode 2 reruns every segment from its initial state with output, and a sequence's last segment writes the pool.
-template <typename T>
+// portion from the pool's state.  Long portions of steps with few CTAs run in three launches so that the segments of one
+// sequence run side by side: mode 1 runs every segment but a sequence's last from a ZERO state, without output, and
+// leaves the segment's end state and its summed step sizes in seg_state / seg_dt; ssm_seg_combine_kernel turns those
+// into each segment's true initial state (S_init[k + 1] = exp(-a sum_dt[k]) S_init[k] + S_local[k], the recurrence
+// being linear in S); mode 2 reruns every segment from its initial state with output, and a sequence's last segment
+// writes the pool.
+template <typename T, int NPT>
 __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__ xbc, int64_t x_stride,
                                                        const T* __restrict__ proj, int64_t p_stride, int dt_off,
                                                        const float* __restrict__ dt_bias,
                                                        const float* __restrict__ A_log, const float* __restrict__ Dp,
                                                        float* __restrict__ state, StepGeom g, float* __restrict__ y,
                                                        int64_t y_stride, int heads, int groups, int P, int N, int NS,
-                                                       int reserved_slot, int mode, int nseg, int seg,
+                                                       int PT, int reserved_slot, int mode, int nseg, int seg,
                                                        float* __restrict__ seg_state, float* __restrict__ seg_dt) {
-  extern __shared__ float sm[];
-  const int PT = 256 / NS;
-  const int NL = NS * (kNPT + 1);               // padded row of B / C: slice s starts at s * 17
-  float* Bs = sm;                               // [kScanTokens][NL]
-  float* Cs = Bs + kScanTokens * NL;            // [kScanTokens][NL]
-  float* xs = Cs + kScanTokens * NL;            // [kScanTokens][PT]
-  float* ys = xs + kScanTokens * PT;            // [kScanTokens][PT]
-  float* dts = ys + kScanTokens * PT;           // [kScanTokens]
+  extern __shared__ __align__(16) float sm[];
+  const int nthr = blockDim.x;
+  const int PW = 2 * PT;                        // value channels per CTA
+  const int NL = NS * (NPT + kPad);            // staged row of B / C: slice s starts at s * 20
+  const int stage_floats = kScanTokens * (2 * NL + PW);
+  float* stages = sm;                           // two stages of [B rows | C rows | x rows] for kScanTokens tokens
+  float* ys = sm + 2 * stage_floats;            // [kScanTokens][PW]
+  float* dts = ys + kScanTokens * PW;           // [kScanTokens]
   float* dAs = dts + kScanTokens;               // [kScanTokens]
-  const int h = blockIdx.x, b = blockIdx.y / nseg, k = blockIdx.y - b * nseg, p0 = blockIdx.z * PT;
+  const int h = blockIdx.x, b = blockIdx.y / nseg, k = blockIdx.y - b * nseg, p0 = blockIdx.z * PW;
   int t0, n_new, start;
   portion(g, b, t0, n_new, start);
   const int j_begin = mode == 0 ? 0 : k * seg;
@@ -163,75 +223,165 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
   const bool last_seg = j_end == n_new;
   if (mode == 1 && last_seg) return;            // nobody needs the end state of a sequence's last segment early
   const int slot = g.slots[b];
-  const int tid = threadIdx.x, s = tid & (NS - 1), pl = tid / NS, p = p0 + pl;
+  const int tid = threadIdx.x, s = tid & (NS - 1), pl = tid / NS;
   const int inner = heads * P, grp = h / (heads / groups);
   if (slot == reserved_slot) {
     if (mode == 1) return;
-    for (int i = tid; i < (j_end - j_begin) * PT; i += 256) {
-      const int j = i / PT, c = i - j * PT;
+    for (int i = tid; i < (j_end - j_begin) * PW; i += nthr) {
+      const int j = i / PW, c = i - j * PW;
       if (p0 + c < P) y[(int64_t)(t0 + j_begin + j) * y_stride + h * P + p0 + c] = 0.f;
     }
     return;
   }
-  float S[kNPT];
-  float* pool_row = state + (((int64_t)slot * heads + h) * P + p) * N + s * kNPT;
-  float* seg_row = seg_state ? seg_state + ((((int64_t)b * nseg + k) * heads + h) * P + p) * N + s * kNPT : nullptr;
-  const float* init = mode == 2 ? seg_row : ((mode == 0 && start > 0) ? pool_row : nullptr);
+  // the padding of the staged rows and the channels past P are zero for good: the copies below never touch them
+  for (int i = tid; i < 2 * stage_floats; i += nthr) stages[i] = 0.f;
+  __syncthreads();
+  int ns_shift = 0;
+  while ((1 << ns_shift) < NS) ++ns_shift;
+  // B / C rows in 16-byte pieces when every piece is aligned in global memory
+  const bool vec_in = (N & 3) == 0 && (x_stride & 3) == 0 && (inner & 3) == 0 &&
+                      (reinterpret_cast<uintptr_t>(xbc) & 15) == 0;
+  // a chunk's inputs are copied global -> shared asynchronously, one chunk ahead of the arithmetic
+  auto issue = [&](int stage, int c0) {
+    const int nt = min(kScanTokens, j_end - c0);
+    float* Bs = stages + stage * stage_floats;
+    float* Cs = Bs + kScanTokens * NL;
+    float* xs = Cs + kScanTokens * NL;
+    if (vec_in) {      // 16-byte pieces: rows of NS * NPT / 4 pieces (a power of two)
+      const int row_shift = ns_shift + (NPT == 16 ? 2 : 1);
+      for (int i = tid; i < (nt << row_shift); i += nthr) {
+        const int j = i >> row_shift, n = (i & ((1 << row_shift) - 1)) * 4;
+        if (n < N) {
+          const float* row = xbc + (int64_t)(t0 + c0 + j) * x_stride + inner + grp * N;
+          const int at = j * NL + (n / NPT) * (NPT + kPad) + (n % NPT);
+          cp_async16(Bs + at, row + n);
+          cp_async16(Cs + at, row + (int64_t)groups * N + n);
+        }
+      }
+    } else {
+      const int row_shift = ns_shift + (NPT == 16 ? 4 : 3);
+      for (int i = tid; i < (nt << row_shift); i += nthr) {
+        const int j = i >> row_shift, n = i & ((1 << row_shift) - 1);
+        if (n < N) {
+          const float* row = xbc + (int64_t)(t0 + c0 + j) * x_stride + inner + grp * N;
+          const int at = j * NL + (n / NPT) * (NPT + kPad) + (n % NPT);
+          cp_async4(Bs + at, row + n);
+          cp_async4(Cs + at, row + (int64_t)groups * N + n);
+        }
+      }
+    }
+    for (int i = tid; i < nt * PW; i += nthr) {
+      const int j = i / PW, c = i - j * PW;
+      if (p0 + c < P) cp_async4(xs + i, xbc + (int64_t)(t0 + c0 + j) * x_stride + h * P + p0 + c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const bool vec = (N & 3) == 0;                // 16-byte state rows
+  float S[2][NPT];
+  float* pool_row[2];
+  float* seg_row[2];
+  const float* init[2];
+  bool live[2];
 #pragma unroll
-  for (int i = 0; i < kNPT; ++i) S[i] = (init && p < P && s * kNPT + i < N) ? init[i] : 0.f;
+  for (int u = 0; u < 2; ++u) {
+    const int p = p0 + pl + u * PT;
+    live[u] = p < P;
+    pool_row[u] = state + (((int64_t)slot * heads + h) * P + p) * N + s * NPT;
+    seg_row[u] = seg_state ? seg_state + ((((int64_t)b * nseg + k) * heads + h) * P + p) * N + s * NPT : nullptr;
+    init[u] = mode == 2 ? seg_row[u] : ((mode == 0 && start > 0) ? pool_row[u] : nullptr);
+  }
+  issue(0, j_begin);
+  float dt_next = (tid < min(kScanTokens, j_end - j_begin))
+                      ? to_f<T>(proj[(int64_t)(t0 + j_begin + tid) * p_stride + dt_off + h]) : 0.f;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    if (init[u] && live[u] && vec) {
+#pragma unroll
+      for (int i = 0; i < NPT; i += 4) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s * NPT + i < N) v = *reinterpret_cast<const float4*>(init[u] + i);
+        S[u][i] = v.x; S[u][i + 1] = v.y; S[u][i + 2] = v.z; S[u][i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) S[u][i] = (init[u] && live[u] && s * NPT + i < N) ? init[u][i] : 0.f;
+    }
+  }
   const float a = expf(A_log[h]), dsk = Dp[h], bias = dt_bias[h];
   float dt_sum = 0.f;
-  for (int c0 = j_begin; c0 < j_end; c0 += kScanTokens) {
+  int stage = 0;
+  for (int c0 = j_begin; c0 < j_end; c0 += kScanTokens, stage ^= 1) {
     const int nt = min(kScanTokens, j_end - c0);
-    __syncthreads();   // the previous pass's ys / inputs are no longer read
-    for (int i = tid; i < nt * NL; i += 256) {
-      const int j = i / NL, r = i - j * NL, sl = r / (kNPT + 1), kk = r - sl * (kNPT + 1), n = sl * kNPT + kk;
-      const bool in = kk < kNPT && n < N;
-      const float* row = xbc + (int64_t)(t0 + c0 + j) * x_stride + inner + grp * N;
-      Bs[i] = in ? row[n] : 0.f;
-      Cs[i] = in ? row[(int64_t)groups * N + n] : 0.f;
-    }
-    for (int i = tid; i < nt * PT; i += 256) {
-      const int j = i / PT, c = i - j * PT;
-      xs[i] = p0 + c < P ? xbc[(int64_t)(t0 + c0 + j) * x_stride + h * P + p0 + c] : 0.f;
-    }
-    if (tid < nt) {
-      const float dt = softplus_f(to_f<T>(proj[(int64_t)(t0 + c0 + tid) * p_stride + dt_off + h]) + bias);
+    const int c1 = c0 + kScanTokens;
+    if (tid < nt) {               // step sizes of this chunk from the value fetched a chunk ago; fetch the next
+      const float dt = softplus_f(dt_next + bias);
       dts[tid] = dt;
       dAs[tid] = expf(-a * dt);
     }
-    __syncthreads();
-    for (int j = 0; j < nt; ++j) {
-      const float dA = dAs[j], xv = xs[j * PT + pl], dx = dts[j] * xv;
-      const float* Br = Bs + j * NL + s * (kNPT + 1);
-      dt_sum += dts[j];
-      if (mode == 1) {
-#pragma unroll
-        for (int i = 0; i < kNPT; ++i) S[i] = fmaf(dA, S[i], dx * Br[i]);
-        continue;
-      }
-      const float* Cr = Cs + j * NL + s * (kNPT + 1);
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < kNPT; ++i) {
-        S[i] = fmaf(dA, S[i], dx * Br[i]);
-        acc = fmaf(S[i], Cr[i], acc);
-      }
-      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (s == 0) ys[j * PT + pl] = acc + dsk * xv;
+    if (c1 < j_end) {
+      issue(stage ^ 1, c1);       // its stage was last read before the barrier that ended the previous pass
+      if (tid < min(kScanTokens, j_end - c1)) dt_next = to_f<T>(proj[(int64_t)(t0 + c1 + tid) * p_stride + dt_off + h]);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
+    __syncthreads();              // every thread's copies of this chunk have landed; dts / dAs are written
+    const float* Bs = stages + stage * stage_floats;
+    const float* Cs = Bs + kScanTokens * NL;
+    const float* xs = Cs + kScanTokens * NL;
+    for (int j = 0; j < nt; ++j) {
+      const float dA = dAs[j], dt = dts[j];
+      const float x0 = xs[j * PW + pl], x1 = xs[j * PW + pl + PT];
+      const float dx0 = dt * x0, dx1 = dt * x1;
+      dt_sum += dt;
+      const float4* B4 = reinterpret_cast<const float4*>(Bs + j * NL + s * (NPT + kPad));
+      const float4* C4 = reinterpret_cast<const float4*>(Cs + j * NL + s * (NPT + kPad));
+      float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < NPT / 4; ++q) {
+        const float4 bv = B4[q];
+        float4 cv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mode != 1) cv = C4[q];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = q * 4 + e;
+          const float be = f4_at(bv, e), ce = f4_at(cv, e);
+          S[0][i] = fmaf(dA, S[0][i], dx0 * be);
+          S[1][i] = fmaf(dA, S[1][i], dx1 * be);
+          acc0 = fmaf(S[0][i], ce, acc0);
+          acc1 = fmaf(S[1][i], ce, acc1);
+        }
+      }
+      if (mode == 1) continue;
+      for (int o = NS >> 1; o > 0; o >>= 1) {
+        acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
+        acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+      }
+      if (s == 0) {
+        ys[j * PW + pl] = acc0 + dsk * x0;
+        ys[j * PW + pl + PT] = acc1 + dsk * x1;
+      }
+    }
+    __syncthreads();              // ys complete; this chunk's stage and dts may be overwritten from here on
     if (mode == 1) continue;
-    __syncthreads();
-    for (int i = tid; i < nt * PT; i += 256) {
-      const int j = i / PT, c = i - j * PT;
+    for (int i = tid; i < nt * PW; i += nthr) {
+      const int j = i / PW, c = i - j * PW;
       if (p0 + c < P) y[(int64_t)(t0 + c0 + j) * y_stride + h * P + p0 + c] = ys[i];
     }
   }
-  float* dst = mode == 1 ? seg_row : ((mode == 0 || last_seg) ? pool_row : nullptr);
-  if (dst && p < P) {
 #pragma unroll
-    for (int i = 0; i < kNPT; ++i)
-      if (s * kNPT + i < N) dst[i] = S[i];
+  for (int u = 0; u < 2; ++u) {
+    float* dst = mode == 1 ? seg_row[u] : ((mode == 0 || last_seg) ? pool_row[u] : nullptr);
+    if (!dst || !live[u]) continue;
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < NPT; i += 4)
+        if (s * NPT + i < N) *reinterpret_cast<float4*>(dst + i) = make_float4(S[u][i], S[u][i + 1], S[u][i + 2], S[u][i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < NPT; ++i)
+        if (s * NPT + i < N) dst[i] = S[u][i];
+    }
   }
   if (mode == 1 && tid == 0 && blockIdx.z == 0) seg_dt[((int64_t)b * nseg + k) * heads + h] = dt_sum;
 }
@@ -285,17 +435,34 @@ __global__ void __launch_bounds__(128) gated_group_norm_kernel(const float* __re
   for (int i = threadIdx.x; i < part; i += 128) out[t * o_stride + c0 + i] = from_f<T>(vals[i] * inv * w[c0 + i]);
 }
 
+// state channels per thread: 8 (twice the threads, for the latencies of a sequential recurrence) up to N = 256, else 16
+int scan_npt(int N) { return N <= 256 ? 8 : 16; }
+
 int scan_slices(int N) {
+  const int npt = scan_npt(N);
   int ns = 1;
-  while (ns * kNPT < N) ns <<= 1;
+  while (ns * npt < N) ns <<= 1;
   return ns;
 }
 
+// value channels per thread row: 256 / NS, but no more than half the head's channels need (a thread owns two)
+int scan_rows(int NS, int P) {
+  int pt = 256 / NS;
+  const int need = cdiv(cdiv(P, 2) * NS, 32) * 32 / NS;   // whole warps
+  return need < pt ? (need > 0 ? need : 1) : pt;
+}
+
 // Tokens per segment of a step whose longest portion has max_new tokens; 0 = portions run whole, in one launch.
-// Segments are a multiple of the staging pass; the test option "ssm_segment" overrides the product's 256.
-int scan_segment(int max_new) {
+// Segments cost 1.6x the instructions of the single pass, and with every SM busy the kernel is bound by instruction
+// issue: they pay only when whole portions would leave at least half of the SMs idle.  They are a multiple of the
+// staging pass; the test option "ssm_segment" forces a length whatever the CTA count.
+int scan_segment(int max_new, int B, int heads, int P, int N) {
   int seg = test_options().ssm_segment.load();
-  if (seg <= 0) seg = 256;
+  if (seg <= 0) {
+    const int NS = scan_slices(N);
+    if (2 * (int64_t)B * heads * cdiv(P, 2 * scan_rows(NS, P)) > (int64_t)sm_count()) return 0;
+    seg = 256;
+  }
   seg = cdiv(seg, kScanTokens) * kScanTokens;
   return max_new > seg ? seg : 0;
 }
@@ -319,6 +486,23 @@ extern "C" int cvllm_causal_conv(const void* proj, int64_t proj_stride, int x_of
   CVLLM_CHECK_SUPPORTED(taps <= kMaxTaps && B <= 65535 && cdiv(channels, 128) <= 65535);
   auto st = static_cast<cudaStream_t>(stream);
   const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
+  if (taps >= 2 && taps <= 4) {
+    const dim3 rgrid(cdiv(max_new, kConvRun), B, cdiv(channels, 128));
+#define CVLLM_CONV(T, TAPS)                                                                                     \
+  causal_conv_run_kernel<T, TAPS><<<rgrid, 128, 0, st>>>(static_cast<const T*>(proj), proj_stride, x_off, channels, \
+                                                         weight, bias, static_cast<const T*>(conv_state), g, out,  \
+                                                         out_stride)
+    if (dtype == CVLLM_BF16) {
+      if (taps == 2) CVLLM_CONV(__nv_bfloat16, 2); else if (taps == 3) CVLLM_CONV(__nv_bfloat16, 3);
+      else CVLLM_CONV(__nv_bfloat16, 4);
+    } else {
+      if (taps == 2) CVLLM_CONV(float, 2); else if (taps == 3) CVLLM_CONV(float, 3);
+      else CVLLM_CONV(float, 4);
+    }
+#undef CVLLM_CONV
+    CVLLM_CHECK_LAUNCH();
+    return CVLLM_OK;
+  }
   const dim3 grid(cdiv(max_new, kConvTokens), B, cdiv(channels, 128));
   if (dtype == CVLLM_BF16)
     causal_conv_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(proj), proj_stride, x_off,
@@ -358,7 +542,7 @@ extern "C" int cvllm_conv_state_update(const void* proj, int64_t proj_stride, in
 }
 
 extern "C" size_t cvllm_ssm_scan_workspace_bytes(int B, int max_new, int heads, int P, int N) {
-  const int seg = scan_segment(max_new);
+  const int seg = scan_segment(max_new, B, heads, P, N);
   if (seg <= 0) return 0;
   const size_t nseg = (size_t)cdiv(max_new, seg);
   return sizeof(float) * (size_t)B * nseg * heads * ((size_t)P * N + 1);
@@ -376,10 +560,10 @@ extern "C" int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* 
   CVLLM_CHECK_ARG(cu_seqlens_q ? seq_start != nullptr : (positions != nullptr && max_new == 1));
   const int NS = scan_slices(N);
   CVLLM_CHECK_SUPPORTED(NS <= 32);
-  const int PT = 256 / NS;
+  const int PT = scan_rows(NS, P);
   auto st = static_cast<cudaStream_t>(stream);
   const StepGeom g{cu_seqlens_q, seq_start, positions, batch_mapping};
-  const int seg = scan_segment(max_new);
+  const int seg = scan_segment(max_new, B, heads, P, N);
   const int nseg = seg > 0 ? cdiv(max_new, seg) : 1;
   CVLLM_CHECK_SUPPORTED((int64_t)B * nseg <= 65535);
   float* seg_state = nullptr;
@@ -392,15 +576,19 @@ extern "C" int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* 
     seg_state = workspace;
     seg_dt = workspace + (size_t)B * nseg * heads * P * N;
   }
-  const dim3 grid(heads, B * nseg, cdiv(P, PT));
-  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * NS * (kNPT + 1) + 2 * kScanTokens * PT + 2 * kScanTokens);
-  static std::atomic<uint64_t> mask_b{0}, mask_f{0};
+  const dim3 grid(heads, B * nseg, cdiv(P, 2 * PT));
+  const int threads = PT * NS;
+  // two stages of (B rows, C rows, x rows) + the output rows + step sizes and decays
+  const int npt = scan_npt(N);
+  const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * (2 * NS * (npt + kPad) + 2 * PT) +
+                                       (size_t)kScanTokens * 2 * PT + 2 * kScanTokens);
+  static std::atomic<uint64_t> mask_b[2], mask_f[2];   // per kernel instance: [8 | 16 state channels per thread]
 #define CVLLM_SCAN(T, MASK, MODE)                                                                                  \
   do {                                                                                                             \
-    auto kern = ssm_scan_kernel<T>;                                                                                \
-    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, MASK)); \
-    kern<<<grid, 256, smem, st>>>(xbc, xbc_stride, static_cast<const T*>(proj), proj_stride, dt_off, dt_bias, A_log, D, \
-                                  state, g, y, y_stride, heads, groups, P, N, NS, reserved_slot, MODE, nseg,      \
+    auto kern = npt == 8 ? ssm_scan_kernel<T, 8> : ssm_scan_kernel<T, 16>;                                                                             \
+    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, MASK[npt == 16])); \
+    kern<<<grid, threads, smem, st>>>(xbc, xbc_stride, static_cast<const T*>(proj), proj_stride, dt_off, dt_bias, A_log, D, \
+                                  state, g, y, y_stride, heads, groups, P, N, NS, PT, reserved_slot, MODE, nseg,  \
                                   seg > 0 ? seg : max_new, seg_state, seg_dt);                                     \
     CVLLM_CHECK_LAUNCH();                                                                                          \
   } while (0)
