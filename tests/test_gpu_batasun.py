@@ -4,8 +4,6 @@ Every test makes its own small configuration and random weights.  The engine run
 (`ModelRunner.run_step`, the paged cache, the state pool, the native kernels); the oracle recomputes whole sequences
 without a cache or a carried state.  float32 runs are compared sharply (they show a key that is one position off or a
 state that was lost), bfloat16 runs loosely."""
-import math
-
 import pytest
 import torch
 
@@ -556,6 +554,7 @@ def test_a_request_left_out_of_steps_goes_on_later():
      (latent(1, 6, 2, 3, 6, 4, kv_from=0), moe(6, 9.0, 2, 2, 6, 0.1))],                       # no recurrence; two borrowers
     [(latent(2, 64, 64, 64, 160, 48), None)],                                                 # key rows of 224 numbers
     [(latent(2, 40, 24, 48, 104, 48, base=1e6), moe(24, 1.0, 16, 8, 0)), (mamba(8, 8, 130, 4, 4, 8), None)],
+    [(mamba(2, 8, 260, 1, 7, 2), None), (mamba(1, 70, 18, 1, 16, 5), None)],    # 16 state channels per thread; 16 taps
 ])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_other_sizes(layers, dtype):
