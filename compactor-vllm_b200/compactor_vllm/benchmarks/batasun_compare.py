@@ -146,9 +146,13 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
                                                       N.ptr(pos_all), N.ptr(q_full), q_full.stride(0), la.row, la.kv_rank,
                                                       L, code, st), "q_rope")),
         nbytes=2 * L * H * 2 * la.rot_dim, like="qknorm_store")
-    add("bias_attn_varlen, values in keys (4096 tokens, 32 heads, rows of 128, values of 96)",
-        timed(lambda: attn.attend(q_full)), flops=2.0 * (la.row + la.kv_rank) * H * L * (L + 1) / 2,
-        like="bias_attn_varlen_mma")
+    add("portion attention, values in keys (4096 tokens, 32 heads, rows of 128, values of 96; tcgen05 pipeline with "
+        "the whole row as the value)", timed(lambda: attn.attend(q_full)),
+        flops=2.0 * (la.row + la.kv_rank) * H * L * (L + 1) / 2, like="prefill_attn_bias")
+    N.set_test_option("bias_attn_fma", 2)
+    add("portion attention, values in keys (the same on the mma.sync kernel)", timed(lambda: attn.attend(q_full)),
+        flops=2.0 * (la.row + la.kv_rank) * H * L * (L + 1) / 2, like="bias_attn_varlen_mma")
+    N.set_test_option("bias_attn_fma", 0)
     o = torch.randn(L, H * la.vdim, device=dev).to(bf)
     gsrc = torch.randn(L, H * la.vdim, device=dev).to(bf)
     add("sigmoid_gate (4096 x 2048)", timed(lambda: sigmoid_gate(o, gsrc)), nbytes=6 * L * H * la.vdim, like="gated_act")
@@ -189,10 +193,10 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
     pre = (N.ptr(cu), N.ptr(st0), None, N.ptr(bm1))
     add("causal_conv (4096 tokens, 10240 channels)", timed(lambda: conv(pre, 1, L)), nbytes=L * C * (2 + 4),
         like="qknorm_store")
-    add("ssm_scan (one portion of 4096 tokens, segments of 256)", timed(lambda: scan(pre, 1, L)),
+    add("ssm_scan (one portion of 4096 tokens, the product's choice: whole portions at this CTA count)", timed(lambda: scan(pre, 1, L)),
         nbytes=4 * L * (C + mx.inner), like="bias_attn_varlen (the mixer's portion kernel)")
-    N.set_test_option("ssm_segment", 1 << 20)
-    add("ssm_scan (one portion of 4096 tokens, one CTA per head)", timed(lambda: scan(pre, 1, L)),
+    N.set_test_option("ssm_segment", 256)
+    add("ssm_scan (one portion of 4096 tokens, forced segments of 256)", timed(lambda: scan(pre, 1, L)),
         nbytes=4 * L * (C + mx.inner), like="bias_attn_varlen (the mixer's portion kernel)")
     N.set_test_option("ssm_segment", 0)
     add("gated_group_norm (4096 x 8192)",

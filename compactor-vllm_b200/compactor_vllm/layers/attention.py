@@ -180,8 +180,9 @@ class BiasedChunkAttention(nn.Module):
             *table, N.ptr(self.bh_seq_lens), T, H, G, D, Dv, RESERVED_BATCH, code, N.stream(dev)), "cvllm_qknorm_store")
         return self.attend(q)
 
-    def attend(self, q: torch.Tensor) -> torch.Tensor:
-        """q [T, H, D] (normed / rotated already, the step's keys in the cache) -> [T, H * Dv]."""
+    def attend(self, q: torch.Tensor, flat: bool = True) -> torch.Tensor:
+        """q [T, H, D] (normed / rotated already, the step's keys in the cache) -> [T, H * Dv], or with flat=False
+        [T, H, Dv] (possibly a view of wider rows)."""
         from compactor_vllm import _native as N
 
         ctx: Context = get_context()
@@ -192,6 +193,13 @@ class BiasedChunkAttention(nn.Module):
         pt = self.page_table
         table = (N.ptr(pt), pt.stride(0), pt.stride(1), int(self.page_size))
         v_cache, v_stride = (self.k_cache, D) if self.values_in_keys else (self.v_cache, Dv)
+        keep = Dv
+        if (self.values_in_keys and ctx.is_prefill and q.dtype == torch.bfloat16 and D == 128 and Dv < D
+                and self.page_size % 128 == 0 and (H // G) % 2 == 0):
+            # Values that are columns of 128-wide key rows: taking the WHOLE row as the value costs a few more
+            # products and puts the portion on the tcgen05 pipeline (which serves D = Dv = 128); the columns past
+            # the values are dropped on return.
+            Dv = D
         out = torch.empty((T, H, Dv), dtype=q.dtype, device=dev)
         if ctx.is_prefill:
             B = ctx.batch_mapping.numel()
@@ -209,4 +217,7 @@ class BiasedChunkAttention(nn.Module):
                 N.ptr(ctx.batch_mapping), N.ptr(self.slopes), self.chunk, int(self.sink), self.scale, N.ptr(out),
                 T, H, G, D, Dv, RESERVED_BATCH, splits, N.ptr(ws), ws.numel() if ws is not None else 0, v_stride, code,
                 N.stream(dev)), "cvllm_bias_attn_decode")
-        return out.view(T, H * Dv)
+        if keep != Dv:
+            out = out[:, :, :keep]
+            return out.reshape(T, H * keep) if flat else out
+        return out.view(T, H * Dv) if flat else out

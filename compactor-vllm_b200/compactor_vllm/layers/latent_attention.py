@@ -97,7 +97,7 @@ class LatentAttention(nn.Module):
         torch.bmm(q[:, :, :D].transpose(0, 1), self.uk, out=q_full[:, :, :r].transpose(0, 1))
         N.check(lib.cvllm_latent_q_rope(N.ptr(q), q.stride(0), H, D, R, N.ptr(self.inv_freq), N.ptr(ctx.positions_i32),
                                         N.ptr(q_full), q_full.stride(0), self.row, r, T, code, st), "cvllm_latent_q_rope")
-        o_lat = attn.attend(q_full).view(T, H, r)
+        o_lat = attn.attend(q_full, flat=False)           # [T, H, r], possibly a view of wider rows
         o = torch.empty((T, H, Dv), dtype=proj.dtype, device=dev)
         torch.bmm(o_lat.transpose(0, 1), self.uv.transpose(1, 2), out=o.transpose(0, 1))
         return self.o_proj(sigmoid_gate(o.view(T, H * Dv), proj[:, self.g_off:]))

@@ -546,6 +546,30 @@ def test_a_request_left_out_of_steps_goes_on_later():
     assert rel_err(torch.cat(out_b), O.forward(om, b)) < TOL["float32"]
 
 
+def test_latent_rows_of_128_on_the_tcgen05_pipeline():
+    """bfloat16 portions with key rows of 128 numbers and pages of 128 tokens take the tcgen05 portion kernel with the
+    whole row as the value (the columns past the values are dropped): against the mma.sync kernel on the same inputs
+    (test option) and against the oracle, with portions cut off the 128-row tiles and a borrowing layer."""
+    from compactor_vllm import _native as N
+    from oracle import batasun as O
+
+    cfg = model_cfg([(latent(4, 64, 32, 64, 96, 64, base=1e4), None), (latent(2, 32, 32, 48, 96, 32, base=1e4, kv_from=0), None)],
+                    vocab=64, width=64)
+    r = make_runner(cfg, "bfloat16", pages=6, page_size=128)
+    toks = tokens(400, 64, 12)
+    want = O.forward(oracle_model(r.model), toks)
+    got = {}
+    for name, option in (("tcgen05", 0), ("mma", 2)):
+        N.set_test_option("bias_attn_fma", option)
+        try:
+            got[name] = [run_in_portions(r, toks, sizes).float().cpu() for sizes in ([400], [130, 127, 143], [257, 2, 141])]
+        finally:
+            N.set_test_option("bias_attn_fma", 0)
+    for a, b in zip(got["tcgen05"], got["mma"]):
+        assert close(a, want, "bfloat16")
+        assert rel_err(a, b.double()) < 3e-2
+
+
 # ------------------------------------------------------------------------------------------------------ other sizes
 @pytest.mark.parametrize("layers", [
     [(mamba(1, 4, 1, 1, 1, 1), moe(4, 1.0, 1, 1, 4, 1.0))],                                   # everything 1
