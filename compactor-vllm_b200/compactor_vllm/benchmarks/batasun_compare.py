@@ -18,7 +18,7 @@ from compactor_vllm.benchmarks.arch_compare import (DECODE_BATCH, DECODE_CONTEXT
                                                     _events_ms, engine_throughput, movolorn_config)
 
 # the latent sizes the tensor-core portion kernel serves: key rows of kv_rank + rot_dim = 128 numbers
-LATENT = dict(dim=64, rot_dim=32, vdim=64, kv_rank=96)
+LATENT = dict(dim=128, rot_dim=64, vdim=128, kv_rank=64)
 STATE, VDIM, CONV = 128, 64, 4
 
 
@@ -103,7 +103,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
     add("moe_route (top logits)", timed(lambda: route(lg, None, 6, 1, 1, ROUTE_TOP_LOGITS, experts=E)),
         nbytes=4 * T * 4 * (E + 1 + 12), like="moe_route (softmax, groups)")
     del lg
-    # --- latent attention, 32 heads over one latent row of 96 + 32 numbers
+    # --- latent attention, 32 heads over one latent row of 64 + 64 numbers
     H = 32
     prev = torch.get_default_dtype()
     torch.set_default_dtype(bf)          # as the runner builds models: 16-bit matrices, fp32 gains, 64-bit frequencies
@@ -146,7 +146,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
                                                       N.ptr(pos_all), N.ptr(q_full), q_full.stride(0), la.row, la.kv_rank,
                                                       L, code, st), "q_rope")),
         nbytes=2 * L * H * 2 * la.rot_dim, like="qknorm_store")
-    add("portion attention, values in keys (4096 tokens, 32 heads, rows of 128, values of 96; tcgen05 pipeline with "
+    add("portion attention, values in keys (4096 tokens, 32 heads, rows of 128, values of 64; tcgen05 pipeline with "
         "the whole row as the value)", timed(lambda: attn.attend(q_full)),
         flops=2.0 * (la.row + la.kv_rank) * H * L * (L + 1) / 2, like="prefill_attn_bias")
     N.set_test_option("bias_attn_fma", 2)
@@ -155,7 +155,7 @@ def kernel_rooflines(peaks: dict, reps: int) -> List[dict]:
     N.set_test_option("bias_attn_fma", 0)
     o = torch.randn(L, H * la.vdim, device=dev).to(bf)
     gsrc = torch.randn(L, H * la.vdim, device=dev).to(bf)
-    add("sigmoid_gate (4096 x 2048)", timed(lambda: sigmoid_gate(o, gsrc)), nbytes=6 * L * H * la.vdim, like="gated_act")
+    add(f"sigmoid_gate (4096 x {H * la.vdim})", timed(lambda: sigmoid_gate(o, gsrc)), nbytes=6 * L * H * la.vdim, like="gated_act")
     B = 8
     set_context(is_prefill=False, batch_mapping=i32(slots), positions_i32=i32([L - 1] * B), token_slot=i32(slots),
                 max_seqlen_q=1, max_seqlen_k=L)

@@ -182,8 +182,6 @@ __device__ __forceinline__ void cp_async16(float* smem, const float* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem) : "memory");
 }
 
-__device__ __forceinline__ float f4_at(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
-
 // grid (heads, B * nseg, value tiles), PT * NS threads: NS slices of the state dimension (a power of two, NS * 16 >= N)
 // times PT value channels; thread (pl, s) keeps S[p, 16 s .. 16 s + 15] for its TWO value channels p = p0 + pl and
 // p0 + pl + PT in registers over its tokens, so that the 32 values of B_t and C_t it reads from shared memory per token
@@ -196,7 +194,7 @@ __device__ __forceinline__ float f4_at(const float4& v, int i) { return i == 0 ?
 // into each segment's true initial state (S_init[k + 1] = exp(-a sum_dt[k]) S_init[k] + S_local[k], the recurrence
 // being linear in S); mode 2 reruns every segment from its initial state with output, and a sequence's last segment
 // writes the pool.
-template <typename T, int NPT>
+template <typename T, int NPT, bool WITH_Y>
 __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__ xbc, int64_t x_stride,
                                                        const T* __restrict__ proj, int64_t p_stride, int dt_off,
                                                        const float* __restrict__ dt_bias,
@@ -277,7 +275,7 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const bool vec = (N & 3) == 0;                // 16-byte state rows
-  float S[2][NPT];
+  float2 S[2][NPT / 2];          // pairs of neighbouring state channels: the arithmetic below is packed fp32x2
   float* pool_row[2];
   float* seg_row[2];
   const float* init[2];
@@ -300,11 +298,16 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
       for (int i = 0; i < NPT; i += 4) {
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (s * NPT + i < N) v = *reinterpret_cast<const float4*>(init[u] + i);
-        S[u][i] = v.x; S[u][i + 1] = v.y; S[u][i + 2] = v.z; S[u][i + 3] = v.w;
+        S[u][i / 2] = make_float2(v.x, v.y);
+        S[u][i / 2 + 1] = make_float2(v.z, v.w);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) S[u][i] = (init[u] && live[u] && s * NPT + i < N) ? init[u][i] : 0.f;
+      for (int i = 0; i < NPT; i += 2) {
+        const bool ok = init[u] && live[u];
+        S[u][i / 2] = make_float2((ok && s * NPT + i < N) ? init[u][i] : 0.f,
+                                  (ok && s * NPT + i + 1 < N) ? init[u][i + 1] : 0.f);
+      }
     }
   }
   const float a = expf(A_log[h]), dsk = Dp[h], bias = dt_bias[h];
@@ -336,23 +339,28 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
       dt_sum += dt;
       const float4* B4 = reinterpret_cast<const float4*>(Bs + j * NL + s * (NPT + kPad));
       const float4* C4 = reinterpret_cast<const float4*>(Cs + j * NL + s * (NPT + kPad));
-      float acc0 = 0.f, acc1 = 0.f;
+      // per pair of state channels: S = dA S + (dt x) B  (a product rounded, then one FMA) and y += S C, as fp32x2
+      const float2 dA2 = make_float2(dA, dA), dxa = make_float2(dx0, dx0), dxb = make_float2(dx1, dx1);
+      float2 a0 = make_float2(0.f, 0.f), a1 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int q = 0; q < NPT / 4; ++q) {
         const float4 bv = B4[q];
-        float4 cv = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (mode != 1) cv = C4[q];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = q * 4 + e;
-          const float be = f4_at(bv, e), ce = f4_at(cv, e);
-          S[0][i] = fmaf(dA, S[0][i], dx0 * be);
-          S[1][i] = fmaf(dA, S[1][i], dx1 * be);
-          acc0 = fmaf(S[0][i], ce, acc0);
-          acc1 = fmaf(S[1][i], ce, acc1);
+        const float2 b01 = make_float2(bv.x, bv.y), b23 = make_float2(bv.z, bv.w);
+        S[0][2 * q] = __ffma2_rn(dA2, S[0][2 * q], __fmul2_rn(dxa, b01));
+        S[0][2 * q + 1] = __ffma2_rn(dA2, S[0][2 * q + 1], __fmul2_rn(dxa, b23));
+        S[1][2 * q] = __ffma2_rn(dA2, S[1][2 * q], __fmul2_rn(dxb, b01));
+        S[1][2 * q + 1] = __ffma2_rn(dA2, S[1][2 * q + 1], __fmul2_rn(dxb, b23));
+        if constexpr (WITH_Y) {
+          const float4 cv = C4[q];
+          const float2 c01 = make_float2(cv.x, cv.y), c23 = make_float2(cv.z, cv.w);
+          a0 = __ffma2_rn(S[0][2 * q], c01, a0);
+          a0 = __ffma2_rn(S[0][2 * q + 1], c23, a0);
+          a1 = __ffma2_rn(S[1][2 * q], c01, a1);
+          a1 = __ffma2_rn(S[1][2 * q + 1], c23, a1);
         }
       }
-      if (mode == 1) continue;
+      if constexpr (!WITH_Y) continue;
+      float acc0 = a0.x + a0.y, acc1 = a1.x + a1.y;
       for (int o = NS >> 1; o > 0; o >>= 1) {
         acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
         acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
@@ -376,11 +384,15 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
     if (vec) {
 #pragma unroll
       for (int i = 0; i < NPT; i += 4)
-        if (s * NPT + i < N) *reinterpret_cast<float4*>(dst + i) = make_float4(S[u][i], S[u][i + 1], S[u][i + 2], S[u][i + 3]);
+        if (s * NPT + i < N)
+          *reinterpret_cast<float4*>(dst + i) =
+              make_float4(S[u][i / 2].x, S[u][i / 2].y, S[u][i / 2 + 1].x, S[u][i / 2 + 1].y);
     } else {
 #pragma unroll
-      for (int i = 0; i < NPT; ++i)
-        if (s * NPT + i < N) dst[i] = S[u][i];
+      for (int i = 0; i < NPT; i += 2) {
+        if (s * NPT + i < N) dst[i] = S[u][i / 2].x;
+        if (s * NPT + i + 1 < N) dst[i + 1] = S[u][i / 2].y;
+      }
     }
   }
   if (mode == 1 && tid == 0 && blockIdx.z == 0) seg_dt[((int64_t)b * nseg + k) * heads + h] = dt_sum;
@@ -582,11 +594,12 @@ extern "C" int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* 
   const int npt = scan_npt(N);
   const size_t smem = sizeof(float) * ((size_t)2 * kScanTokens * (2 * NS * (npt + kPad) + 2 * PT) +
                                        (size_t)kScanTokens * 2 * PT + 2 * kScanTokens);
-  static std::atomic<uint64_t> mask_b[2], mask_f[2];   // per kernel instance: [8 | 16 state channels per thread]
+  static std::atomic<uint64_t> mask_b[4], mask_f[4];   // per kernel instance: [8 | 16 state channels per thread][with | without output]
 #define CVLLM_SCAN(T, MASK, MODE)                                                                                  \
   do {                                                                                                             \
-    auto kern = npt == 8 ? ssm_scan_kernel<T, 8> : ssm_scan_kernel<T, 16>;                                                                             \
-    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, MASK[npt == 16])); \
+    auto kern = npt == 8 ? (MODE == 1 ? ssm_scan_kernel<T, 8, false> : ssm_scan_kernel<T, 8, true>)                \
+                         : (MODE == 1 ? ssm_scan_kernel<T, 16, false> : ssm_scan_kernel<T, 16, true>);                                                                             \
+    if (smem > 48 * 1024) CVLLM_CHECK_CUDA(ensure_max_dyn_smem(reinterpret_cast<const void*>(kern), (int)smem, MASK[(npt == 16) * 2 + (MODE == 1)])); \
     kern<<<grid, threads, smem, st>>>(xbc, xbc_stride, static_cast<const T*>(proj), proj_stride, dt_off, dt_bias, A_log, D, \
                                   state, g, y, y_stride, heads, groups, P, N, NS, PT, reserved_slot, MODE, nseg,  \
                                   seg > 0 ? seg : max_new, seg_state, seg_dt);                                     \

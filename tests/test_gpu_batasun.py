@@ -553,7 +553,7 @@ def test_latent_rows_of_128_on_the_tcgen05_pipeline():
     from compactor_vllm import _native as N
     from oracle import batasun as O
 
-    cfg = model_cfg([(latent(4, 64, 32, 64, 96, 64, base=1e4), None), (latent(2, 32, 32, 48, 96, 32, base=1e4, kv_from=0), None)],
+    cfg = model_cfg([(latent(4, 48, 64, 40, 64, 56, base=1e4), None), (latent(2, 32, 64, 24, 64, 32, base=1e4, kv_from=0), None)],
                     vocab=64, width=64)
     r = make_runner(cfg, "bfloat16", pages=6, page_size=128)
     toks = tokens(400, 64, 12)
