@@ -92,7 +92,7 @@ struct TestOptions {
   std::atomic<uint64_t> grs_debug_host_ptr{0};  // pinned host buffer for gemm_reduce's timeout records
   std::atomic<int> grs_rows_per_round{0};     // > 0: rows per reduce round of gemm_reduce (multiple of 256)
   std::atomic<int> bias_attn_fma{0};          // 1: 16-bit portions of the biased attention on the fp32 FMA kernel
-  std::atomic<int> ssm_segment{0};            // > 0: tokens per segment of the state-space scan (product: 256)
+  std::atomic<int> ssm_segment{0};            // > 0: tokens per segment of the state-space scan (0: chosen per step)
 };
 TestOptions& test_options();
 

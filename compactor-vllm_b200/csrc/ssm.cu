@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(128) conv_state_update_kernel(const T* __restr
 
 constexpr int kScanTokens = 16;   // tokens staged per pass
 
+constexpr int kGroup = 4;         // tokens whose arithmetic is interleaved
 constexpr int kPad = 4;           // floats between the 16-value slices of a staged B / C row (keeps 16-byte alignment)
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
@@ -316,9 +317,9 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
   for (int c0 = j_begin; c0 < j_end; c0 += kScanTokens, stage ^= 1) {
     const int nt = min(kScanTokens, j_end - c0);
     const int c1 = c0 + kScanTokens;
-    if (tid < nt) {               // step sizes of this chunk from the value fetched a chunk ago; fetch the next
-      const float dt = softplus_f(dt_next + bias);
-      dts[tid] = dt;
+    if (tid < kScanTokens) {      // step sizes of this chunk from the value fetched a chunk ago; fetch the next
+      const float dt = tid < nt ? softplus_f(dt_next + bias) : 0.f;
+      dts[tid] = dt;              // past the chunk's end: dt = 0, decay 1
       dAs[tid] = expf(-a * dt);
     }
     if (c1 < j_end) {
@@ -332,42 +333,62 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
     const float* Bs = stages + stage * stage_floats;
     const float* Cs = Bs + kScanTokens * NL;
     const float* xs = Cs + kScanTokens * NL;
-    for (int j = 0; j < nt; ++j) {
-      const float dA = dAs[j], dt = dts[j];
-      const float x0 = xs[j * PW + pl], x1 = xs[j * PW + pl + PT];
-      const float dx0 = dt * x0, dx1 = dt * x1;
-      dt_sum += dt;
-      const float4* B4 = reinterpret_cast<const float4*>(Bs + j * NL + s * (NPT + kPad));
-      const float4* C4 = reinterpret_cast<const float4*>(Cs + j * NL + s * (NPT + kPad));
-      // per pair of state channels: S = dA S + (dt x) B  (a product rounded, then one FMA) and y += S C, as fp32x2
-      const float2 dA2 = make_float2(dA, dA), dxa = make_float2(dx0, dx0), dxb = make_float2(dx1, dx1);
-      float2 a0 = make_float2(0.f, 0.f), a1 = make_float2(0.f, 0.f);
+    // Tokens go in groups of four: the loads and the arithmetic of a group carry no store between them, so the four
+    // tokens' shared-memory loads, FMA chains and cross-lane sums overlap; only S links one token to the next.
+    for (int j0 = 0; j0 < nt; j0 += kGroup) {
+      float r0[kGroup], r1[kGroup], xa[kGroup], xb[kGroup];
 #pragma unroll
-      for (int q = 0; q < NPT / 4; ++q) {
-        const float4 bv = B4[q];
-        const float2 b01 = make_float2(bv.x, bv.y), b23 = make_float2(bv.z, bv.w);
-        S[0][2 * q] = __ffma2_rn(dA2, S[0][2 * q], __fmul2_rn(dxa, b01));
-        S[0][2 * q + 1] = __ffma2_rn(dA2, S[0][2 * q + 1], __fmul2_rn(dxa, b23));
-        S[1][2 * q] = __ffma2_rn(dA2, S[1][2 * q], __fmul2_rn(dxb, b01));
-        S[1][2 * q + 1] = __ffma2_rn(dA2, S[1][2 * q + 1], __fmul2_rn(dxb, b23));
-        if constexpr (WITH_Y) {
-          const float4 cv = C4[q];
-          const float2 c01 = make_float2(cv.x, cv.y), c23 = make_float2(cv.z, cv.w);
-          a0 = __ffma2_rn(S[0][2 * q], c01, a0);
-          a0 = __ffma2_rn(S[0][2 * q + 1], c23, a0);
-          a1 = __ffma2_rn(S[1][2 * q], c01, a1);
-          a1 = __ffma2_rn(S[1][2 * q + 1], c23, a1);
+      for (int u = 0; u < kGroup; ++u) {
+        const int j = j0 + u;                  // rows past nt: dt = 0 and decay 1 leave S as it is
+        const float dA = dAs[j], dt = dts[j];
+        const float x0 = xs[j * PW + pl], x1 = xs[j * PW + pl + PT];
+        const float dx0 = dt * x0, dx1 = dt * x1;
+        xa[u] = x0;
+        xb[u] = x1;
+        dt_sum += dt;
+        const float4* B4 = reinterpret_cast<const float4*>(Bs + j * NL + s * (NPT + kPad));
+        const float4* C4 = reinterpret_cast<const float4*>(Cs + j * NL + s * (NPT + kPad));
+        // per pair of state channels: S = dA S + (dt x) B  (a product rounded, then one FMA) and y += S C, as fp32x2
+        const float2 dA2 = make_float2(dA, dA), dxa = make_float2(dx0, dx0), dxb = make_float2(dx1, dx1);
+        float2 a0 = make_float2(0.f, 0.f), a1 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < NPT / 4; ++q) {
+          const float4 bv = B4[q];
+          const float2 b01 = make_float2(bv.x, bv.y), b23 = make_float2(bv.z, bv.w);
+          S[0][2 * q] = __ffma2_rn(dA2, S[0][2 * q], __fmul2_rn(dxa, b01));
+          S[0][2 * q + 1] = __ffma2_rn(dA2, S[0][2 * q + 1], __fmul2_rn(dxa, b23));
+          S[1][2 * q] = __ffma2_rn(dA2, S[1][2 * q], __fmul2_rn(dxb, b01));
+          S[1][2 * q + 1] = __ffma2_rn(dA2, S[1][2 * q + 1], __fmul2_rn(dxb, b23));
+          if constexpr (WITH_Y) {
+            const float4 cv = C4[q];
+            const float2 c01 = make_float2(cv.x, cv.y), c23 = make_float2(cv.z, cv.w);
+            a0 = __ffma2_rn(S[0][2 * q], c01, a0);
+            a0 = __ffma2_rn(S[0][2 * q + 1], c23, a0);
+            a1 = __ffma2_rn(S[1][2 * q], c01, a1);
+            a1 = __ffma2_rn(S[1][2 * q + 1], c23, a1);
+          }
         }
+        r0[u] = a0.x + a0.y;
+        r1[u] = a1.x + a1.y;
       }
-      if constexpr (!WITH_Y) continue;
-      float acc0 = a0.x + a0.y, acc1 = a1.x + a1.y;
-      for (int o = NS >> 1; o > 0; o >>= 1) {
-        acc0 += __shfl_xor_sync(0xffffffffu, acc0, o);
-        acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
-      }
-      if (s == 0) {
-        ys[j * PW + pl] = acc0 + dsk * x0;
-        ys[j * PW + pl + PT] = acc1 + dsk * x1;
+      if constexpr (WITH_Y) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {     // NS is the same for every thread: no divergence
+          if (o < NS) {
+#pragma unroll
+            for (int u = 0; u < kGroup; ++u) {
+              r0[u] += __shfl_xor_sync(0xffffffffu, r0[u], o);
+              r1[u] += __shfl_xor_sync(0xffffffffu, r1[u], o);
+            }
+          }
+        }
+        if (s == 0) {
+#pragma unroll
+          for (int u = 0; u < kGroup; ++u) {
+            ys[(j0 + u) * PW + pl] = r0[u] + dsk * xa[u];
+            ys[(j0 + u) * PW + pl + PT] = r1[u] + dsk * xb[u];
+          }
+        }
       }
     }
     __syncthreads();              // ys complete; this chunk's stage and dts may be overwritten from here on
@@ -466,14 +487,19 @@ int scan_rows(int NS, int P) {
 
 // Tokens per segment of a step whose longest portion has max_new tokens; 0 = portions run whole, in one launch.
 // Segments cost 1.6x the instructions of the single pass, and with every SM busy the kernel is bound by instruction
-// issue: they pay only when whole portions would leave at least half of the SMs idle.  They are a multiple of the
+// issue: they pay only when whole portions would leave at least half of the SMs idle (measured at 64-channel heads,
+// state 128, 4096 tokens: 16 heads 1.42 -> 0.44 ms, 32 heads 1.49 -> 0.77 ms, 64 heads 1.54 -> 1.34-1.53 ms,
+// 128 heads 1.85 -> 2.5-3.1 ms).  The length aims at three CTAs per SM, is at least 128 tokens and a multiple of the
 // staging pass; the test option "ssm_segment" forces a length whatever the CTA count.
 int scan_segment(int max_new, int B, int heads, int P, int N) {
   int seg = test_options().ssm_segment.load();
   if (seg <= 0) {
     const int NS = scan_slices(N);
-    if (2 * (int64_t)B * heads * cdiv(P, 2 * scan_rows(NS, P)) > (int64_t)sm_count()) return 0;
-    seg = 256;
+    const int64_t ctas = (int64_t)B * heads * cdiv(P, 2 * scan_rows(NS, P));
+    if (2 * ctas > (int64_t)sm_count()) return 0;
+    const int want = (int)((3 * (int64_t)sm_count() + ctas - 1) / ctas);   // segments per portion
+    seg = cdiv(max_new, want);
+    if (seg < 128) seg = 128;
   }
   seg = cdiv(seg, kScanTokens) * kScanTokens;
   return max_new > seg ? seg : 0;

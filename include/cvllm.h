@@ -68,7 +68,7 @@ uint64_t cvllm_launch_count(void);
  *                            2 no UMMA, 4 no stores, 8 no reduce, 16 no L2 hints)
  *   "bias_attn_fma" 0|1|2    bfloat16 portions of cvllm_bias_attn_varlen: 0 product choice, 1 the fp32 FMA kernel,
  *                            2 mma.sync also where the tcgen05 kernel would serve (A/B)
- *   "ssm_segment" n          tokens per segment of cvllm_ssm_scan (0 = the product's 256; tests use short segments)
+ *   "ssm_segment" n          tokens per segment of cvllm_ssm_scan (0 = the product's choice; tests use short segments)
  *   "grs_debug_host_ptr" p   pinned host buffer (64 words per CTA) for cvllm_gemm_allreduce's timeout records
  * Returns CVLLM_E_ARG for an unknown name. */
 int cvllm_set_test_option(const char* name, double value);
@@ -535,8 +535,8 @@ int cvllm_conv_state_update(const void* proj, int64_t proj_stride, int x_off, in
 /* xbc [T, heads * P + 2 * groups * N] fp32 = (x | B | C) after the convolution; dt_raw = proj[t, dt_off + h];
  * state [slots, heads, P, N] fp32, read (portions that start after position 0) and written in place;
  * y [T, heads * P] fp32 = S_t C_t + D_h x_t.  N <= 512.  max_new = the longest portion of the step.  Steps whose
- * longest portion exceeds a segment (256 tokens) run the segments of a sequence side by side in three launches (local
- * end states from zero, a combine pass, the rerun with outputs) and need a workspace of
+ * whole portions would leave half of the SMs idle run the segments (128 tokens or more) of a sequence side by side in
+ * three launches (local end states from zero, a combine pass, the rerun with outputs) and need a workspace of
  * cvllm_ssm_scan_workspace_bytes(B, max_new, heads, P, N) bytes (0 for shorter steps). */
 size_t cvllm_ssm_scan_workspace_bytes(int B, int max_new, int heads, int P, int N);
 int cvllm_ssm_scan(const float* xbc, int64_t xbc_stride, const void* proj, int64_t proj_stride, int dt_off,
