@@ -170,7 +170,8 @@ __global__ void __launch_bounds__(128) conv_state_update_kernel(const T* __restr
 
 constexpr int kScanTokens = 16;   // tokens staged per pass
 
-constexpr int kGroup = 4;         // tokens whose arithmetic is interleaved
+template <int V>
+struct IntC { static constexpr int value = V; };
 constexpr int kPad = 4;           // floats between the 16-value slices of a staged B / C row (keeps 16-byte alignment)
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
@@ -317,9 +318,9 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
   for (int c0 = j_begin; c0 < j_end; c0 += kScanTokens, stage ^= 1) {
     const int nt = min(kScanTokens, j_end - c0);
     const int c1 = c0 + kScanTokens;
-    if (tid < kScanTokens) {      // step sizes of this chunk from the value fetched a chunk ago; fetch the next
-      const float dt = tid < nt ? softplus_f(dt_next + bias) : 0.f;
-      dts[tid] = dt;              // past the chunk's end: dt = 0, decay 1
+    if (tid < nt) {               // step sizes of this chunk from the value fetched a chunk ago; fetch the next
+      const float dt = softplus_f(dt_next + bias);
+      dts[tid] = dt;
       dAs[tid] = expf(-a * dt);
     }
     if (c1 < j_end) {
@@ -335,11 +336,12 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
     const float* xs = Cs + kScanTokens * NL;
     // Tokens go in groups of four: the loads and the arithmetic of a group carry no store between them, so the four
     // tokens' shared-memory loads, FMA chains and cross-lane sums overlap; only S links one token to the next.
-    for (int j0 = 0; j0 < nt; j0 += kGroup) {
+    auto run_group = [&](auto width, int j0) {
+      constexpr int kGroup = decltype(width)::value;
       float r0[kGroup], r1[kGroup], xa[kGroup], xb[kGroup];
 #pragma unroll
       for (int u = 0; u < kGroup; ++u) {
-        const int j = j0 + u;                  // rows past nt: dt = 0 and decay 1 leave S as it is
+        const int j = j0 + u;
         const float dA = dAs[j], dt = dts[j];
         const float x0 = xs[j * PW + pl], x1 = xs[j * PW + pl + PT];
         const float dx0 = dt * x0, dx1 = dt * x1;
@@ -390,7 +392,10 @@ __global__ void __launch_bounds__(256) ssm_scan_kernel(const float* __restrict__
           }
         }
       }
-    }
+    };
+    int j0 = 0;
+    for (; j0 + 4 <= nt; j0 += 4) run_group(IntC<4>{}, j0);
+    for (; j0 < nt; ++j0) run_group(IntC<1>{}, j0);       // a chunk's last tokens, and single-token steps
     __syncthreads();              // ys complete; this chunk's stage and dts may be overwritten from here on
     if (mode == 1) continue;
     for (int i = tid; i < nt * PW; i += nthr) {
