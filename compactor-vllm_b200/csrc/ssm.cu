@@ -493,8 +493,8 @@ int scan_rows(int NS, int P) {
 // Tokens per segment of a step whose longest portion has max_new tokens; 0 = portions run whole, in one launch.
 // Segments cost 1.6x the instructions of the single pass, and with every SM busy the kernel is bound by instruction
 // issue: they pay only when whole portions would leave at least half of the SMs idle (measured at 64-channel heads,
-// state 128, 4096 tokens: 16 heads 1.42 -> 0.44 ms, 32 heads 1.49 -> 0.77 ms, 64 heads 1.54 -> 1.34-1.53 ms,
-// 128 heads 1.85 -> 2.5-3.1 ms).  The length aims at three CTAs per SM, is at least 128 tokens and a multiple of the
+// state 128, 4096 tokens: 16 heads 0.98 -> 0.38 ms, 32 heads 1.04 -> 0.67 ms, 64 heads 1.09 -> 1.18-1.42 ms,
+// 128 heads 1.46 -> 2.2-2.8 ms).  The length aims at three CTAs per SM, is at least 128 tokens and a multiple of the
 // staging pass; the test option "ssm_segment" forces a length whatever the CTA count.
 int scan_segment(int max_new, int B, int heads, int P, int N) {
   int seg = test_options().ssm_segment.load();

@@ -595,6 +595,64 @@ def test_other_sizes(layers, dtype):
     assert close(torch.cat(out), want, dtype)
 
 
+def random_config(seed):
+    """A model drawn at random: 1-5 layers of either mixer in any order, borrowed latents, odd and even sizes."""
+    import random
+
+    rnd = random.Random(seed)
+    pick = lambda *xs: rnd.choice(xs)
+    layers, owners = [], []
+    for i in range(rnd.randint(1, 5)):
+        mlp = None if rnd.random() < 0.3 else moe(pick(5, 8, 12, 16), pick(0.4, 1.0, 6.0), pick(1, 2, 5, 9), 1, pick(0, 7, 16),
+                                                  pick(0.5, 2.0))
+        if mlp is not None:
+            mlp["router"]["top"] = rnd.randint(1, min(4, mlp["router"]["experts"]))
+        if rnd.random() < 0.5:
+            heads, vdim = pick(1, 2, 3, 4, 6), pick(3, 8, 10, 16, 24)
+            groups = pick(*[g for g in (1, 2, 3, 4, 6) if heads % g == 0])
+            parts = pick(*[k for k in (1, 2, 3, 4) if (heads * vdim) % k == 0])
+            layers.append((mamba(heads, vdim, pick(1, 5, 16, 24, 40, 70), groups, pick(1, 2, 3, 4, 6), parts), mlp))
+        elif owners and rnd.random() < 0.4:
+            j = pick(*owners)
+            o = layers[j][0]["mixer"]
+            layers.append((latent(pick(1, 2, 5), pick(4, 8, 14), o["rot_dim"], pick(4, 9, 16), o["kv_rank"], pick(3, 8, 20),
+                                  base=o["rot"]["base"], kv_from=j), mlp))
+        else:
+            owners.append(i)
+            layers.append((latent(pick(1, 2, 3, 4), pick(4, 8, 14, 32), pick(2, 4, 8, 16), pick(4, 9, 16, 32),
+                                  pick(6, 16, 24, 48, 112), pick(3, 8, 20), base=pick(10.0, 1e4, 5e5),
+                                  scale=pick(0.1, 0.3)), mlp))
+    return model_cfg(layers, vocab=pick(37, 64, 101), width=pick(24, 40, 64), eps=pick(1e-6, 1e-5, 1e-3))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_configurations(seed):
+    """Whatever config.json says is what runs: whole prompts, portions with single tokens between them, decoding from
+    the graph, two requests in one batch."""
+    from oracle import batasun as O
+
+    cfg = random_config(seed)
+    r = make_runner(cfg, "float32", pages=16, page_size=16, eager=False)
+    om = oracle_model(r.model)
+    V = cfg["vocab"]
+    a, b = tokens(50, V, 100 + seed), tokens(21, V, 200 + seed)
+    wa, wb = O.forward(om, a), O.forward(om, b)
+    assert rel_err(run_in_portions(r, a, [50]), wa) < TOL["float32"]
+    assert rel_err(run_in_portions(r, a, [9, 1, 1, 17, 2]), wa) < TOL["float32"]
+    sa, sb = new_seq(), new_seq()
+    out_a, out_b = [], []
+    for lo_a, hi_a, lo_b, hi_b in ((0, 30, 0, 1), (30, 31, 1, 2), (31, 50, 2, 21)):
+        sa.prompt_token_ids.extend(a[lo_a:hi_a])
+        sb.prompt_token_ids.extend(b[lo_b:hi_b])
+        na, nb = hi_a - lo_a, hi_b - lo_b
+        logits = r.run_step([(sa, a[lo_a:hi_a]), (sb, b[lo_b:hi_b])], rows=list(range(na + nb)))
+        out_a.append(logits[:na])
+        out_b.append(logits[na:])
+    r.release([sa, sb])
+    assert rel_err(torch.cat(out_a), wa) < TOL["float32"]
+    assert rel_err(torch.cat(out_b), wb) < TOL["float32"]
+
+
 def test_config_refuses_a_bad_borrowed_latent():
     from compactor_vllm.config.model_config import BatasunConfig
 
